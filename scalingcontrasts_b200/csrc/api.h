@@ -1,0 +1,137 @@
+// Host-side entry points of the native layer. Plain C++ types only, so that the kernel translation units need no
+// framework headers; bindings.cpp wraps these for Python.
+//
+// Every launcher enqueues on the given stream and returns without synchronising. Errors that the host can see at
+// launch time throw std::runtime_error; errors that only the device can see (a wait that ran out) land in the status
+// block passed to the kernel.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include <cuda_runtime.h>
+
+namespace sc {
+
+constexpr int max_prefixes = 8;
+
+struct ladder_host {
+    uint32_t count;
+    uint32_t ends[max_prefixes];
+};
+
+// Number of kernels of this library launched so far by this process (for the bench's launch accounting).
+uint64_t launch_count();
+void note_launch(uint64_t launches = 1);
+
+// -------- collectives (collectives.cu) ---------------------------------------------------------------------------
+// The control block of one member: its own replica's counters, and how to reach everyone's arrival flag.
+struct control_view {
+    uint32_t* multicast_flag;        // multicast alias of the arrival flag; null in a peer (non-multicast) domain
+    uint32_t* own_flag;              // this member's copy of the arrival flag
+    uint32_t* own_round;             // arrivals this member has consumed
+    uint32_t* own_finished;          // blocks of the running kernel that are done
+    uint32_t* status;                // status block (status_words words)
+    uint32_t* peer_flags[16];        // every member's arrival flag as seen from this GPU (peer domain)
+    uint32_t members;
+    uint32_t member;
+    uint64_t budget_ns;
+};
+
+enum class payload_type : int { f32 = 0, bf16 = 1 };
+
+void launch_barrier(control_view const& control, cudaStream_t stream);
+// In place over `scalars` elements starting at element offset `first` of the payload. `multicast` is the multicast
+// alias of the payload (null in a peer domain, where `replicas` lists every member's copy). `scale` multiplies the
+// reduced value before it is stored.
+void launch_all_reduce(control_view const& control, void* multicast, void* const* replicas, size_t first,
+                       size_t scalars, payload_type type, float scale, int multiprocessors, cudaStream_t stream);
+// Member m ends with the reduced elements [first + m*shard, first + (m+1)*shard) in its own replica. When
+// `out_f32` is not null the shard goes there instead (as float32, scaled), leaving the payload untouched.
+void launch_reduce_scatter(control_view const& control, void* multicast, void* const* replicas, void* own, size_t first,
+                           size_t shard_scalars, payload_type type, float scale, float* out_f32, int multiprocessors,
+                           cudaStream_t stream);
+// Makes a wait of this member run out on purpose: consumes one round that nobody arrives for. Host-driven test hook
+// for the timeout path; uses a flag that nothing sets, never a fault.
+void launch_expect_arrivals(control_view const& control, uint32_t arrivals, cudaStream_t stream);
+void preload_collective_kernels();
+
+// -------- small loss kernels (loss_small.cu) ---------------------------------------------------------------------
+void launch_prefix_norms(void const* rows_bf16, void* copy_bf16, float* inverse_norms, float* tile_max, uint32_t rows,
+                         uint32_t hidden, ladder_host const& ladder, cudaStream_t stream);
+void launch_transpose(void const* rows_bf16, void* transposed_bf16, uint32_t rows, uint32_t hidden, cudaStream_t stream);
+void launch_pull(void const* src0, void* dst0, size_t bytes0, void const* src1, void* dst1, size_t bytes1, int blocks,
+                 cudaStream_t stream);
+void launch_fold_partials(float const* partials, float* row_accumulators, uint32_t rows, uint32_t slots,
+                          uint32_t quantities, cudaStream_t stream);
+void launch_finalize(void const* queries_bf16, float const* inverse_norms, float const* row_accumulators,
+                     float const* query_gradient, void* gradient_out_bf16, uint32_t rows, uint32_t hidden,
+                     ladder_host const& ladder, cudaStream_t stream);
+void launch_sum_summands(float const* row_accumulators, float* summands, uint32_t rows, uint32_t prefixes,
+                         cudaStream_t stream);
+void launch_keyed_embeddings(void* rows_bf16, uint32_t rows, uint32_t hidden, uint64_t salt, float scale,
+                             cudaStream_t stream);
+void launch_keyed_integers(float* out, size_t scalars, size_t first, uint32_t members, uint32_t member,
+                           cudaStream_t stream);
+void launch_keyed_fractions(float* out, size_t scalars, size_t first, uint32_t members, uint32_t member,
+                            cudaStream_t stream);
+void launch_count_wrong_sums(float const* values, size_t scalars, size_t first, uint32_t members,
+                             unsigned long long* counter, cudaStream_t stream);
+void launch_count_differences(float const* values, float const* expected, size_t scalars, unsigned long long* counter,
+                              cudaStream_t stream);
+void launch_scale_cast(float const* src, void* dst_bf16, size_t scalars, float scale, cudaStream_t stream);
+
+// -------- tile kernels (loss_fwd.cu, loss_bwd.cu) ----------------------------------------------------------------
+struct pull_request {
+    void const* src[2];
+    void* dst[2];
+    size_t bytes[2]; // multiples of 16
+};
+
+struct forward_arguments {
+    void const* queries_bf16;        // [rows_q, hidden], local memory
+    void const* candidates_bf16;     // [rows_c, hidden], local memory (a staged copy when the block is a peer's)
+    float const* query_inverse_norms;     // [K, rows_q]
+    float const* candidate_inverse_norms; // [K, rows_c]
+    float const* candidate_tile_max;      // [K, rows_c / 64]
+    void* gradient_cube_bf16;        // [K, rows_q, rows_c]
+    float* partials;                 // [slots, quantities, rows_q]
+    uint32_t* status;
+    uint32_t rows_q, rows_c, hidden;
+    ladder_host ladder;
+    uint32_t tiles_per_run;
+    float beta, bias, weight;
+    uint64_t query_base, candidate_base;
+    uint32_t spec_code;
+    uint64_t budget_ns;
+    pull_request pull;               // optional: bytes == 0 means nothing to pull
+    int multiprocessors;
+};
+// Returns the number of partial slots the launch fills: 2 * rows_c / 64 / tiles_per_run.
+uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run);
+uint32_t forward_quantities(uint32_t prefixes);
+uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors);
+void launch_forward(forward_arguments const& arguments, cudaStream_t stream);
+
+struct backward_arguments {
+    void const* gradient_cube_bf16;     // [K, rows_q, rows_c]
+    void const* transposed_candidates;  // [hidden, rows_c]
+    float* query_gradient;              // [rows_q, hidden], accumulated
+    uint32_t* status;
+    uint32_t rows_q, rows_c, hidden;
+    ladder_host ladder;
+    uint32_t split;                     // candidate-range splits (1: deterministic read-modify-write)
+    uint64_t budget_ns;
+};
+void launch_backward(backward_arguments const& arguments, cudaStream_t stream);
+
+void preload_loss_kernels();
+
+// -------- oracle twin (oracle_cpu.cpp) ---------------------------------------------------------------------------
+// Plain triple loop in float64; gradient [n, hidden]; out[0]=loss, out[1]=bias grad, out[2]=log-beta grad,
+// out[4+k]=loss of prefix k.
+void oracle_loops_f64(double const* world, size_t n, size_t hidden, ladder_host const& ladder, double beta, double bias,
+                      uint32_t spec_code, double* gradient, double* out);
+
+} // namespace sc

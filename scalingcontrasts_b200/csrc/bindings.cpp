@@ -1,0 +1,275 @@
+// Python bindings of the native layer. Pointers cross as integers (device addresses, possibly inside symmetric
+// memory that torch does not own), streams as the integer handle torch reports; the Python wrappers validate shapes,
+// dtypes and contiguity before calling in.
+#include <torch/extension.h>
+
+#include <atomic>
+#include <memory>
+
+#include "api.h"
+#include "domain.h"
+#include "rail.h"
+
+namespace py = pybind11;
+
+namespace sc {
+
+namespace {
+std::atomic<uint64_t> launches{0};
+}
+uint64_t launch_count() { return launches.load(); }
+void note_launch(uint64_t count) { launches.fetch_add(count); }
+
+} // namespace sc
+
+namespace {
+
+template <typename T>
+T* pointer(uint64_t address) {
+    return reinterpret_cast<T*>(static_cast<uintptr_t>(address));
+}
+cudaStream_t stream_of(uint64_t handle) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(handle)); }
+
+sc::ladder_host ladder_of(std::vector<uint32_t> const& ends) {
+    if (ends.empty() || ends.size() > sc::max_prefixes) throw std::runtime_error("a ladder holds 1..8 prefixes");
+    sc::ladder_host ladder{};
+    ladder.count = static_cast<uint32_t>(ends.size());
+    for (size_t i = 0; i < ends.size(); ++i) ladder.ends[i] = ends[i];
+    return ladder;
+}
+
+// Byte offsets of the control words inside a replica's control block.
+constexpr uint64_t control_flag = 0, control_round = 16, control_finished = 32, control_status = 64;
+
+struct control_handle {
+    sc::control_view view{};
+    std::vector<void*> replicas; // every member's replica base, for the peer path
+    uint64_t multicast_base = 0;
+    uint64_t own_base = 0;
+};
+
+std::shared_ptr<control_handle> make_control(sc::native_domain const& domain, uint64_t control_offset, uint64_t budget_ns,
+                                             bool use_multicast) {
+    auto handle = std::make_shared<control_handle>();
+    uint64_t const own = domain.replica(domain.member()) + control_offset;
+    handle->view.own_flag = pointer<uint32_t>(own + control_flag);
+    handle->view.own_round = pointer<uint32_t>(own + control_round);
+    handle->view.own_finished = pointer<uint32_t>(own + control_finished);
+    handle->view.status = pointer<uint32_t>(own + control_status);
+    handle->view.multicast_flag =
+        use_multicast && domain.has_multicast() ? pointer<uint32_t>(domain.multicast() + control_offset + control_flag) : nullptr;
+    handle->view.members = static_cast<uint32_t>(domain.members());
+    handle->view.member = static_cast<uint32_t>(domain.member());
+    handle->view.budget_ns = budget_ns;
+    for (int m = 0; m < domain.members(); ++m) {
+        handle->view.peer_flags[m] = pointer<uint32_t>(domain.replica(m) + control_offset + control_flag);
+        handle->replicas.push_back(pointer<void>(domain.replica(m)));
+    }
+    handle->multicast_base = use_multicast && domain.has_multicast() ? domain.multicast() : 0;
+    handle->own_base = domain.replica(domain.member());
+    return handle;
+}
+
+torch::Tensor tensor_from_pointer(uint64_t address, std::vector<int64_t> sizes, std::string const& dtype, int device) {
+    torch::ScalarType type;
+    if (dtype == "float32") type = torch::kFloat32;
+    else if (dtype == "bfloat16") type = torch::kBFloat16;
+    else if (dtype == "uint8") type = torch::kUInt8;
+    else if (dtype == "int32") type = torch::kInt32;
+    else if (dtype == "int64") type = torch::kInt64;
+    else throw std::runtime_error("tensor_from_pointer: unsupported dtype " + dtype);
+    auto options = torch::TensorOptions().dtype(type).device(torch::kCUDA, device);
+    return torch::from_blob(pointer<void>(address), sizes, [](void*) {}, options);
+}
+
+} // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "sm_100a kernels and the symmetric-memory domain of scalingcontrasts_b200";
+    m.def("launch_count", &sc::launch_count);
+    m.def("tensor_from_pointer", &tensor_from_pointer);
+    m.attr("CONTROL_BYTES") = 256;
+    m.attr("STATUS_OFFSET") = control_status;
+    m.attr("ROUND_OFFSET") = control_round;
+    m.attr("FLAG_OFFSET") = control_flag;
+    m.attr("FINISHED_OFFSET") = control_finished;
+
+    py::class_<sc::native_domain, std::shared_ptr<sc::native_domain>>(m, "NativeDomain")
+        .def(py::init<int, int, int, size_t, bool>())
+        .def_static("multicast_supported", &sc::native_domain::multicast_supported)
+        .def("export_replica", &sc::native_domain::export_replica)
+        .def("import_replica", &sc::native_domain::import_replica)
+        .def("create_multicast", &sc::native_domain::create_multicast)
+        .def("import_multicast", &sc::native_domain::import_multicast)
+        .def("add_device", &sc::native_domain::add_device)
+        .def("map_replicas", &sc::native_domain::map_replicas)
+        .def("bind_multicast", &sc::native_domain::bind_multicast)
+        .def("zero_own", &sc::native_domain::zero_own)
+        .def("close", &sc::native_domain::close)
+        .def("replica", &sc::native_domain::replica)
+        .def("multicast", &sc::native_domain::multicast)
+        .def("stride", &sc::native_domain::stride)
+        .def("has_multicast", &sc::native_domain::has_multicast)
+        .def("members", &sc::native_domain::members)
+        .def("member", &sc::native_domain::member);
+
+    py::class_<control_handle, std::shared_ptr<control_handle>>(m, "Control")
+        .def("set_budget_ns", [](control_handle& c, uint64_t ns) { c.view.budget_ns = ns; })
+        .def("budget_ns", [](control_handle const& c) { return c.view.budget_ns; })
+        .def("uses_multicast", [](control_handle const& c) { return c.view.multicast_flag != nullptr; });
+    m.def("make_control", &make_control);
+    m.def("preload_kernels", []() {
+        sc::preload_collective_kernels();
+        sc::preload_loss_kernels();
+    });
+
+    m.def("barrier", [](control_handle const& c, uint64_t stream) { sc::launch_barrier(c.view, stream_of(stream)); });
+    m.def("expect_arrivals", [](control_handle const& c, uint32_t arrivals, uint64_t stream) {
+        sc::launch_expect_arrivals(c.view, arrivals, stream_of(stream));
+    });
+    m.def("all_reduce", [](control_handle const& c, uint64_t byte_offset, uint64_t scalars, int type, float scale, int sms,
+                           uint64_t stream) {
+        auto const kind = static_cast<sc::payload_type>(type);
+        uint64_t const width = kind == sc::payload_type::f32 ? 4 : 2;
+        if (byte_offset % 16) throw std::runtime_error("all_reduce: the payload must start on a 16-byte boundary");
+        // Offsets are applied to the base pointers so that `first` stays zero and element indices stay small.
+        std::vector<void*> replicas;
+        for (void* base : c.replicas) replicas.push_back(static_cast<char*>(base) + byte_offset);
+        void* multicast = c.multicast_base ? pointer<void>(c.multicast_base + byte_offset) : nullptr;
+        (void)width;
+        sc::launch_all_reduce(c.view, multicast, replicas.data(), 0, scalars, kind, scale, sms, stream_of(stream));
+    });
+    m.def("reduce_scatter", [](control_handle const& c, uint64_t byte_offset, uint64_t shard_scalars, int type, float scale,
+                               uint64_t out_f32, int sms, uint64_t stream) {
+        auto const kind = static_cast<sc::payload_type>(type);
+        if (byte_offset % 16) throw std::runtime_error("reduce_scatter: the payload must start on a 16-byte boundary");
+        std::vector<void*> replicas;
+        for (void* base : c.replicas) replicas.push_back(static_cast<char*>(base) + byte_offset);
+        void* multicast = c.multicast_base ? pointer<void>(c.multicast_base + byte_offset) : nullptr;
+        sc::launch_reduce_scatter(c.view, multicast, replicas.data(), pointer<void>(c.own_base + byte_offset), 0, shard_scalars,
+                                  kind, scale, pointer<float>(out_f32), sms, stream_of(stream));
+    });
+
+    m.def("prefix_norms", [](uint64_t rows, uint64_t copy, uint64_t inverse_norms, uint64_t tile_max, uint32_t row_count,
+                             uint32_t hidden, std::vector<uint32_t> const& ends, uint64_t stream) {
+        sc::launch_prefix_norms(pointer<void>(rows), pointer<void>(copy), pointer<float>(inverse_norms), pointer<float>(tile_max),
+                                row_count, hidden, ladder_of(ends), stream_of(stream));
+    });
+    m.def("transpose", [](uint64_t rows, uint64_t out, uint32_t row_count, uint32_t hidden, uint64_t stream) {
+        sc::launch_transpose(pointer<void>(rows), pointer<void>(out), row_count, hidden, stream_of(stream));
+    });
+    m.def("pull", [](uint64_t src0, uint64_t dst0, uint64_t bytes0, uint64_t src1, uint64_t dst1, uint64_t bytes1, int blocks,
+                     uint64_t stream) {
+        sc::launch_pull(pointer<void>(src0), pointer<void>(dst0), bytes0, pointer<void>(src1), pointer<void>(dst1), bytes1, blocks,
+                        stream_of(stream));
+    });
+    m.def("fold_partials", [](uint64_t partials, uint64_t accumulators, uint32_t rows, uint32_t slots, uint32_t quantities,
+                              uint64_t stream) {
+        sc::launch_fold_partials(pointer<float>(partials), pointer<float>(accumulators), rows, slots, quantities, stream_of(stream));
+    });
+    m.def("finalize", [](uint64_t queries, uint64_t inverse_norms, uint64_t accumulators, uint64_t query_gradient, uint64_t out,
+                         uint32_t rows, uint32_t hidden, std::vector<uint32_t> const& ends, uint64_t stream) {
+        sc::launch_finalize(pointer<void>(queries), pointer<float>(inverse_norms), pointer<float>(accumulators),
+                            pointer<float>(query_gradient), pointer<void>(out), rows, hidden, ladder_of(ends), stream_of(stream));
+    });
+    m.def("sum_summands", [](uint64_t accumulators, uint64_t summands, uint32_t rows, uint32_t prefixes, uint64_t stream) {
+        sc::launch_sum_summands(pointer<float>(accumulators), pointer<float>(summands), rows, prefixes, stream_of(stream));
+    });
+    m.def("forward_partial_slots", &sc::forward_partial_slots);
+    m.def("forward_quantities", &sc::forward_quantities);
+    m.def("forward_choose_tiles_per_run", &sc::forward_choose_tiles_per_run);
+    m.def("forward",
+          [](uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t cube,
+             uint64_t partials, uint64_t status, uint32_t rows_q, uint32_t rows_c, uint32_t hidden,
+             std::vector<uint32_t> const& ends, uint32_t tiles_per_run, float beta, float bias, float weight, uint64_t query_base,
+             uint64_t candidate_base, uint32_t spec_code, uint64_t budget_ns, uint64_t pull_src0, uint64_t pull_dst0,
+             uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1, int sms, uint64_t stream) {
+              sc::forward_arguments a{};
+              a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
+              a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
+              a.candidate_tile_max = pointer<float>(c_tile_max);
+              a.gradient_cube_bf16 = pointer<void>(cube), a.partials = pointer<float>(partials);
+              a.status = pointer<uint32_t>(status);
+              a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends);
+              a.tiles_per_run = tiles_per_run, a.beta = beta, a.bias = bias, a.weight = weight;
+              a.query_base = query_base, a.candidate_base = candidate_base, a.spec_code = spec_code, a.budget_ns = budget_ns;
+              a.pull.src[0] = pointer<void>(pull_src0), a.pull.dst[0] = pointer<void>(pull_dst0), a.pull.bytes[0] = pull_bytes0;
+              a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;
+              a.multiprocessors = sms;
+              sc::launch_forward(a, stream_of(stream));
+          });
+    m.def("backward", [](uint64_t cube, uint64_t transposed, uint64_t query_gradient, uint64_t status, uint32_t rows_q,
+                         uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, uint64_t budget_ns,
+                         uint64_t stream) {
+        sc::backward_arguments a{};
+        a.gradient_cube_bf16 = pointer<void>(cube), a.transposed_candidates = pointer<void>(transposed);
+        a.query_gradient = pointer<float>(query_gradient), a.status = pointer<uint32_t>(status);
+        a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends), a.split = split;
+        a.budget_ns = budget_ns;
+        sc::launch_backward(a, stream_of(stream));
+    });
+
+    m.def("keyed_embeddings", [](uint64_t rows, uint32_t row_count, uint32_t hidden, uint64_t salt, float scale, uint64_t stream) {
+        sc::launch_keyed_embeddings(pointer<void>(rows), row_count, hidden, salt, scale, stream_of(stream));
+    });
+    m.def("keyed_integers", [](uint64_t out, uint64_t scalars, uint64_t first, uint32_t members, uint32_t member, uint64_t stream) {
+        sc::launch_keyed_integers(pointer<float>(out), scalars, first, members, member, stream_of(stream));
+    });
+    m.def("keyed_fractions", [](uint64_t out, uint64_t scalars, uint64_t first, uint32_t members, uint32_t member, uint64_t stream) {
+        sc::launch_keyed_fractions(pointer<float>(out), scalars, first, members, member, stream_of(stream));
+    });
+    m.def("count_wrong_sums", [](uint64_t values, uint64_t scalars, uint64_t first, uint32_t members, uint64_t counter,
+                                 uint64_t stream) {
+        sc::launch_count_wrong_sums(pointer<float>(values), scalars, first, members, pointer<unsigned long long>(counter),
+                                    stream_of(stream));
+    });
+    m.def("count_differences", [](uint64_t values, uint64_t expected, uint64_t scalars, uint64_t counter, uint64_t stream) {
+        sc::launch_count_differences(pointer<float>(values), pointer<float>(expected), scalars,
+                                     pointer<unsigned long long>(counter), stream_of(stream));
+    });
+    m.def("scale_cast", [](uint64_t src, uint64_t dst, uint64_t scalars, float scale, uint64_t stream) {
+        sc::launch_scale_cast(pointer<float>(src), pointer<void>(dst), scalars, scale, stream_of(stream));
+    });
+
+    py::class_<sc::loopback_rail, std::shared_ptr<sc::loopback_rail>>(m, "LoopbackRail")
+        .def(py::init<int, uint64_t, uint64_t, uint64_t, int, int, std::string const&, uint32_t>())
+        .def("local_endpoint",
+             [](sc::loopback_rail const& rail) {
+                 return py::bytes(reinterpret_cast<char const*>(&rail.local()), sizeof(sc::rail_endpoint));
+             })
+        .def("connect",
+             [](sc::loopback_rail& rail, std::string const& endpoint) {
+                 if (endpoint.size() != sizeof(sc::rail_endpoint)) throw std::runtime_error("rail: malformed endpoint record");
+                 sc::rail_endpoint remote;
+                 std::memcpy(&remote, endpoint.data(), sizeof(remote));
+                 rail.connect(remote);
+             })
+        .def("post_embeddings", &sc::loopback_rail::post_embeddings)
+        .def("post_summands",
+             [](sc::loopback_rail& rail, int row, std::vector<float> const& values) {
+                 if (values.size() != 4) throw std::runtime_error("rail: a summands row holds four floats");
+                 rail.post_summands(row, values.data());
+             })
+        .def("await_landed", &sc::loopback_rail::await_landed, py::call_guard<py::gil_scoped_release>())
+        .def("read_summands",
+             [](sc::loopback_rail const& rail, int row) {
+                 std::vector<float> out(4);
+                 rail.read_summands(row, out.data());
+                 return out;
+             })
+        .def("inject_completion_error", &sc::loopback_rail::inject_completion_error)
+        .def("drain", &sc::loopback_rail::drain)
+        .def("close", &sc::loopback_rail::close)
+        .def("posted", &sc::loopback_rail::posted)
+        .def("consumed", &sc::loopback_rail::consumed);
+    m.attr("ENDPOINT_BYTES") = sizeof(sc::rail_endpoint);
+
+    m.def("oracle_loops", [](torch::Tensor world, std::vector<uint32_t> const& ends, double beta, double bias, uint32_t spec_code) {
+        auto w = world.to(torch::kFloat64).contiguous().cpu();
+        auto gradient = torch::zeros_like(w);
+        auto out = torch::zeros({12}, torch::kFloat64);
+        sc::oracle_loops_f64(w.data_ptr<double>(), w.size(0), w.size(1), ladder_of(ends), beta, bias, spec_code,
+                             gradient.data_ptr<double>(), out.data_ptr<double>());
+        return std::make_tuple(gradient, out);
+    });
+}

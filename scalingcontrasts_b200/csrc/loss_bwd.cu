@@ -1,0 +1,234 @@
+// Backward tile kernel of the streamed loss: folds a block's per-band gradient cubes into the owner's rows,
+//   query_gradient[i, h] += sum_j G_band(h)[i, j] * candidate[j, h],
+// as tcgen05 GEMM tiles of 128 rows x up to 192 channels, the candidate index as the K dimension in stages of 64.
+// A channel tile never crosses a band edge (edges are multiples of 16 channels and a tile is a multiple of 16 wide),
+// so its A operand is a single band's cube. Candidates arrive transposed ([H, R], K-major rows of candidates), the
+// cube through a three-dimensional TMA map.
+//
+// Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lanes 32*w..), warp 4 TMA producer, warp 5 UMMA issuer
+// and tensor-memory owner. With `split == 1` each output element is touched by exactly one CTA per launch (plain
+// read-modify-write, deterministic); with a larger split the candidate range is divided and partial sums are added
+// with atomics.
+//
+// Parity: backward_tile_cuda_ (scalingcontrasts.cuh:1042-1136).
+#include <stdexcept>
+#include <string>
+
+#include "api.h"
+#include "common.cuh"
+#include "driver.h"
+
+namespace sc {
+
+namespace {
+
+constexpr uint32_t bwd_rows = 128;
+constexpr uint32_t bwd_depth = 64;        // candidates per stage
+constexpr uint32_t bwd_max_width = 192;   // channels per tile
+constexpr uint32_t bwd_stages = 4;
+constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;
+constexpr uint32_t bwd_b_bytes = bwd_max_width * bwd_depth * 2;
+constexpr uint32_t bwd_stage_bytes = bwd_a_bytes + bwd_b_bytes;
+constexpr uint32_t bwd_tmem_columns = 256;
+constexpr uint32_t bwd_threads = 192;
+constexpr uint32_t bwd_max_tiles = 32;
+
+struct bwd_tail {
+    uint64_t stage_full[bwd_stages];
+    uint64_t stage_empty[bwd_stages];
+    uint64_t accumulated;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+constexpr uint32_t bwd_shared_bytes = 1024 + bwd_stages * bwd_stage_bytes + sizeof(bwd_tail);
+
+struct bwd_tile {
+    uint32_t band, channel0, width;
+};
+
+struct bwd_params {
+    float* query_gradient;
+    uint32_t* status;
+    uint32_t rows_q, rows_c, hidden;
+    uint32_t tile_count, split;
+    uint64_t budget_ns;
+    bwd_tile tiles[bwd_max_tiles];
+};
+
+__global__ void __launch_bounds__(bwd_threads, 1)
+    backward_kernel(const __grid_constant__ CUtensorMap cube_map, const __grid_constant__ CUtensorMap candidates_map,
+                    const bwd_params p) {
+    extern __shared__ uint8_t raw_shared[];
+    uint32_t const raw_address = smem_u32(raw_shared);
+    uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
+    bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + bwd_stages * bwd_stage_bytes);
+    uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    bwd_tile const tile = p.tiles[blockIdx.x];
+    uint32_t const strip = blockIdx.y;
+    uint32_t const chunks_total = p.rows_c / bwd_depth;
+    uint32_t const chunks_per_split = (chunks_total + p.split - 1) / p.split;
+    uint32_t const chunk_begin = min(blockIdx.z * chunks_per_split, chunks_total);
+    uint32_t const chunk_end = min(chunk_begin + chunks_per_split, chunks_total);
+
+    if (threadIdx.x == 0) {
+        tail->abort_flag = status_poisoned(p.status) ? 1u : 0u;
+        for (uint32_t i = 0; i < bwd_stages; ++i) {
+            mbar_init(smem_u32(&tail->stage_full[i]), 1);
+            mbar_init(smem_u32(&tail->stage_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&tail->accumulated), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (tail->abort_flag != 0u || chunk_begin >= chunk_end) return;
+    if (warp == 5) {
+        tmem_alloc(smem_u32(&tail->tmem_base), bwd_tmem_columns);
+        tmem_relinquish();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_descriptor(&cube_map);
+        tma_prefetch_descriptor(&candidates_map);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    uint32_t const tmem_base = tail->tmem_base;
+    wait_context const ctx{p.status, p.budget_ns, &tail->abort_flag};
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t const bytes = bwd_a_bytes + tile.width * bwd_depth * 2;
+            for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+                if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_bwd_stage_empty, chunk)) break;
+                uint32_t const full = smem_u32(&tail->stage_full[stage]);
+                uint32_t const destination = stages_base + stage * bwd_stage_bytes;
+                mbar_arrive_expect_tx(full, bytes);
+                tma_load_3d(destination, &cube_map, full, static_cast<int>(chunk * bwd_depth), static_cast<int>(strip * bwd_rows),
+                            static_cast<int>(tile.band));
+                for (uint32_t r = 0; r < tile.width / 16; ++r)
+                    tma_load_2d(destination + bwd_a_bytes + r * 2048u, &candidates_map, full, static_cast<int>(chunk * bwd_depth),
+                                static_cast<int>(tile.channel0 + r * 16));
+                if (++stage == bwd_stages) stage = 0, phase ^= 1u;
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width);
+            uint32_t stage = 0, phase = 0, accumulate = 0;
+            bool ok = true;
+            for (uint32_t chunk = chunk_begin; chunk < chunk_end && ok; ++chunk) {
+                ok = mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_bwd_stage_full, chunk);
+                if (!ok) break;
+                tcgen05_fence_after();
+                uint32_t const a_address = stages_base + stage * bwd_stage_bytes;
+#pragma unroll
+                for (uint32_t step = 0; step < bwd_depth / 16; ++step) {
+                    umma_bf16(tmem_base, umma_desc_k_major_sw128(a_address + step * 32u, 1024u),
+                              umma_desc_k_major_sw128(a_address + bwd_a_bytes + step * 32u, 1024u), idesc, accumulate);
+                    accumulate = 1;
+                }
+                umma_commit(smem_u32(&tail->stage_empty[stage]));
+                if (++stage == bwd_stages) stage = 0, phase ^= 1u;
+            }
+            if (ok) umma_commit(smem_u32(&tail->accumulated));
+        }
+    } else {
+        if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.x)) {
+            tcgen05_fence_after();
+            uint32_t const row = strip * bwd_rows + warp * 32 + lane;
+            float* destination = p.query_gradient + static_cast<size_t>(row) * p.hidden + tile.channel0;
+            uint32_t const lane_base = tmem_base + ((warp * 32u) << 16);
+            for (uint32_t column = 0; column < tile.width; column += 16) {
+                uint32_t values[16];
+                tmem_load_16(lane_base + column, values);
+                tmem_load_wait();
+                if (p.split == 1) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        float4* address = reinterpret_cast<float4*>(destination + column) + v;
+                        float4 current = *address;
+                        current.x += __uint_as_float(values[4 * v]);
+                        current.y += __uint_as_float(values[4 * v + 1]);
+                        current.z += __uint_as_float(values[4 * v + 2]);
+                        current.w += __uint_as_float(values[4 * v + 3]);
+                        *address = current;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) atomicAdd(destination + column + c, __uint_as_float(values[c]));
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tail->abort_flag != 0u) {
+        uint64_t const start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 5) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, bwd_tmem_columns);
+    }
+}
+
+CUtensorMap encode(void const* base, uint32_t rank, cuuint64_t const* dims, cuuint64_t const* strides, cuuint32_t const* box) {
+    CUtensorMap map;
+    cuuint32_t const element_strides[3] = {1, 1, 1};
+    SC_DRIVER(cuTensorMapEncodeTiled, &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box,
+              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return map;
+}
+
+} // namespace
+
+void launch_backward(backward_arguments const& a, cudaStream_t stream) {
+    if (a.rows_q % bwd_rows || a.rows_c % bwd_depth || a.hidden % 16)
+        throw std::runtime_error("backward: rows must be multiples of 128 (queries) and 64 (candidates)");
+    if (a.split < 1) throw std::runtime_error("backward: split must be at least 1");
+    bwd_params p{};
+    p.query_gradient = a.query_gradient, p.status = a.status;
+    p.rows_q = a.rows_q, p.rows_c = a.rows_c, p.hidden = a.hidden;
+    p.split = a.split, p.budget_ns = a.budget_ns;
+    uint32_t begin = 0;
+    for (uint32_t band = 0; band < a.ladder.count; ++band) {
+        uint32_t const end = a.ladder.ends[band];
+        if (end % 16 || end <= begin) throw std::runtime_error("backward: band edges must ascend in multiples of 16");
+        for (uint32_t channel = begin; channel < end; channel += bwd_max_width) {
+            if (p.tile_count == bwd_max_tiles) throw std::runtime_error("backward: too many channel tiles for one launch");
+            uint32_t const width = end - channel < bwd_max_width ? end - channel : bwd_max_width;
+            p.tiles[p.tile_count++] = bwd_tile{band, channel, width};
+        }
+        begin = end;
+    }
+    cuuint64_t const cube_dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
+    cuuint64_t const cube_strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
+    cuuint32_t const cube_box[3] = {bwd_depth, bwd_rows, 1};
+    CUtensorMap const cube_map = encode(a.gradient_cube_bf16, 3, cube_dims, cube_strides, cube_box);
+    cuuint64_t const candidate_dims[2] = {a.rows_c, a.hidden};
+    cuuint64_t const candidate_strides[1] = {static_cast<cuuint64_t>(a.rows_c) * 2};
+    cuuint32_t const candidate_box[2] = {bwd_depth, 16};
+    CUtensorMap const candidates_map = encode(a.transposed_candidates, 2, candidate_dims, candidate_strides, candidate_box);
+
+    require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
+            "raising the backward kernel's shared memory");
+    dim3 const grid(p.tile_count, a.rows_q / bwd_rows, a.split);
+    backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates_map, p);
+    cudaError_t const error = cudaGetLastError();
+    if (error != cudaSuccess) throw std::runtime_error(std::string("backward launch failed: ") + cudaGetErrorString(error));
+    note_launch();
+}
+
+void preload_forward_kernels();
+
+void preload_loss_kernels() {
+    cudaFuncAttributes attributes;
+    require(cudaFuncGetAttributes(&attributes, backward_kernel), "preload backward");
+    preload_forward_kernels();
+}
+
+} // namespace sc

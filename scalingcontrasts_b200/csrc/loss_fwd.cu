@@ -1,0 +1,512 @@
+// Forward tile kernel of the streamed Matryoshka sigmoid loss: scores a block of candidates against this rank's rows at
+// every prefix, applies the sigmoid loss cell by cell, and leaves per band the suffix-summed gradient with respect to
+// the raw dot product (bfloat16) plus per-row partial sums. Optionally the same launch pulls the NEXT peer's block
+// from that peer's memory into local staging, so the NVLink transfer hides under this block's tensor-core work.
+//
+// Shape of the work. A tile is 128 query rows x 64 candidates. The hidden axis streams through shared memory in
+// stages of 64 channels (TMA, 128-byte swizzle), widest channels first. Every band of the ladder owns one 64-column
+// slot of tensor memory and the UMMAs of a 16-channel step accumulate into the slot of the band that contains the
+// step, so each channel is multiplied exactly once (depth H per cell, where a sweep-and-subtract scheme spends up to
+// 2H). The eight slots form a ring: while the epilogue warps drain the K slots of tile t, the issuing thread already
+// fills the widest bands of tile t+1. The epilogue reads the K segment dots of a cell, prefix-sums them into the K
+// prefix dots, runs the cell math and suffix-sums the K gradients, all in registers.
+//
+// Warp roles (384 threads): warps 0-7 epilogue (warp w owns tensor-memory lanes 32*(w%4).. and column half w/4),
+// warp 8 TMA producer, warp 9 UMMA issuer and tensor-memory owner, warps 10-11 peer pull (plain 16-byte loads from
+// the peer's replica, plain stores to local staging; never a TMA load from another GPU's memory).
+//
+// A CTA walks work items (row strip, run of consecutive candidate tiles) in a fixed round-robin order and writes one
+// partial record per (run, column half, row): the fold over runs happens later in run order, so the loss summands do
+// not depend on scheduling.
+//
+// Parity: forward_tile_cuda_ and score_forward_row_ (scalingcontrasts.cuh:688-1040) and fold of its row partials;
+// the staging copy of streamed_loss_t::score (scalingcontrasts.cuh:1262-1265) is what the pull warps replace.
+#include <stdexcept>
+#include <string>
+
+#include "api.h"
+#include "common.cuh"
+#include "driver.h"
+
+namespace sc {
+
+namespace {
+
+constexpr uint32_t fwd_rows = 128;
+constexpr uint32_t fwd_cols = 64;
+constexpr uint32_t fwd_depth = 64;
+constexpr uint32_t fwd_stages = 6;
+constexpr uint32_t fwd_slots = 8;
+constexpr uint32_t fwd_slot_columns = 64;
+constexpr uint32_t fwd_tmem_columns = 512;
+constexpr uint32_t fwd_epilogue_warps = 8;
+constexpr uint32_t fwd_producer_warp = 8;
+constexpr uint32_t fwd_mma_warp = 9;
+constexpr uint32_t fwd_first_pull_warp = 10;
+constexpr uint32_t fwd_pull_warps = 2;
+constexpr uint32_t fwd_threads = 32 * (fwd_epilogue_warps + 2 + fwd_pull_warps);
+constexpr uint32_t fwd_q_bytes = fwd_rows * fwd_depth * 2;
+constexpr uint32_t fwd_c_bytes = fwd_cols * fwd_depth * 2;
+constexpr uint32_t fwd_stage_bytes = fwd_q_bytes + fwd_c_bytes;
+constexpr uint32_t fwd_tile_barriers = 8;
+constexpr float log2_e = 1.4426950408889634f;
+
+struct fwd_tail {
+    uint64_t stage_full[fwd_stages];
+    uint64_t stage_empty[fwd_stages];
+    uint64_t slot_empty[fwd_slots];
+    uint64_t tile_full[fwd_tile_barriers];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+constexpr uint32_t fwd_shared_bytes = 1024 + fwd_stages * fwd_stage_bytes + sizeof(fwd_tail);
+
+struct fwd_params {
+    float const* q_inv;
+    float const* c_inv;
+    float const* c_tile_max;
+    __nv_bfloat16* cube;
+    float* partials;
+    uint32_t* status;
+    uint32_t rows_q, rows_c, hidden;
+    ladder_t ladder;
+    uint32_t tiles_per_run, runs_per_strip, items;
+    float beta, bias, weight;
+    uint64_t query_base, candidate_base;
+    uint32_t spec_code;
+    uint64_t budget_ns;
+    pull_request pull;
+};
+
+// ---- the cell math ----------------------------------------------------------------------------------------------
+// Accumulators are kept without the 1/N weight: `g` sums -mask*z*(1-sigmoid(s)), `ga` sums that times (logit+bias),
+// `loss` sums mask*softplus(-s); the weight is applied once when the partial record is written.
+struct row_constants {
+    float beta, bias, weight, two_beta_weight;
+};
+
+// A negative cell whose cosine is off the floor: z = -1, s = -(logit + bias).
+__device__ __forceinline__ float cell_fast(float prefix_dot, float inv_c, float row_beta, float row_gain, float bias,
+                                           float& loss, float& g, float& ga, float& coefficient) {
+    float const t = prefix_dot * inv_c;
+    float const a = fmaf(t, row_beta, bias);             // logit + bias
+    float const e = fast_ex2(-fabsf(a) * log2_e);         // exp(-|a|)
+    float const r = fast_rcp(1.0f + e);
+    float const complement = (a >= 0.0f ? 1.0f : e) * r;  // 1 - sigmoid(s) = sigmoid(a)
+    loss += fmaxf(a, 0.0f) + log1p_unit(e);
+    g += complement;
+    ga = fmaf(complement, a, ga);
+    float const raw = complement * inv_c * row_gain;      // d loss / d raw dot, mirror cell included
+    coefficient = fmaf(raw, prefix_dot, coefficient);
+    return raw;
+}
+
+// Any cell: positives, the diagonal, floored cosines.
+__device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, float inv_c, row_constants const& k,
+                                              uint64_t global_row, uint64_t global_column, uint32_t spec_code, float& loss,
+                                              float& g, float& ga, float& coefficient) {
+    bool const own = global_row == global_column;
+    bool const partner = (spec_code & 1u) != 0u && (global_row ^ 1ull) == global_column;
+    uint32_t const diagonal = (spec_code >> 1) & 3u; // 0 own, 1 negative, 2 skip
+    float z = partner ? 1.0f : -1.0f;
+    float mask = 1.0f;
+    if (own) {
+        if (diagonal == 0u) z = 1.0f;
+        if (diagonal == 2u) mask = 0.0f;
+    }
+    float const inverse_denominator = fminf(inv_q * inv_c, 100.0f);
+    bool const floored = inverse_denominator >= 100.0f;
+    float const cosine = floored ? 0.0f : prefix_dot * inverse_denominator;
+    float const logit = k.beta * (own ? 1.0f : cosine);
+    float const a = logit + k.bias;
+    float const s = z * a;
+    float const d = fast_ex2(-fabsf(s) * log2_e);
+    float const complement = (s >= 0.0f ? d : 1.0f) * fast_rcp(1.0f + d);
+    float const cell = -mask * z * complement;
+    loss += mask * (fmaxf(-s, 0.0f) + log1p_unit(d));
+    g += cell;
+    ga = fmaf(cell, a, ga);
+    float const raw = (own || floored) ? 0.0f : cell * inverse_denominator * k.two_beta_weight;
+    coefficient = fmaf(raw, prefix_dot, coefficient);
+    return raw;
+}
+
+template <int prefixes_>
+struct fwd_chunk {
+    static constexpr int columns = prefixes_ <= 5 ? 16 : 8;
+};
+
+__device__ __forceinline__ void tmem_load_8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+template <int columns_>
+__device__ __forceinline__ void tmem_load_columns(uint32_t taddr, uint32_t (&r)[columns_]) {
+    if constexpr (columns_ == 16) tmem_load_16(taddr, r);
+    else tmem_load_8(taddr, r);
+}
+
+// ---- roles ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensorMap const* c_map, fwd_params const& p,
+                                              uint32_t stages_base, fwd_tail* tail, wait_context const& ctx) {
+    uint32_t stage = 0, phase = 0;
+    uint32_t const chunks = p.hidden / fwd_depth;
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
+        uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
+        for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
+            uint32_t const column_tile = run * p.tiles_per_run + t;
+            for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
+                if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
+                uint32_t const full = smem_u32(&tail->stage_full[stage]);
+                uint32_t const destination = stages_base + stage * fwd_stage_bytes;
+                mbar_arrive_expect_tx(full, fwd_stage_bytes);
+                tma_load_2d(destination, q_map, full, chunk * static_cast<int>(fwd_depth), static_cast<int>(strip * fwd_rows));
+                tma_load_2d(destination + fwd_q_bytes, c_map, full, chunk * static_cast<int>(fwd_depth),
+                            static_cast<int>(column_tile * fwd_cols));
+                if (++stage == fwd_stages) stage = 0, phase ^= 1u;
+            }
+        }
+    }
+}
+
+template <int prefixes_>
+__device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_base, fwd_tail* tail, uint32_t tmem_base,
+                                         wait_context const& ctx) {
+    constexpr uint32_t idesc = umma_idesc_bf16(fwd_rows, fwd_cols);
+    uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0;
+    int const steps = static_cast<int>(p.hidden / 16);
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
+        for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
+            int band = prefixes_; // none yet
+            uint32_t slot_address = 0, accumulate = 0;
+            for (int step = steps - 1; step >= 0; --step) {
+                uint32_t const sub = static_cast<uint32_t>(step) & 3u;
+                if (sub == 3u) {
+                    if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
+                    tcgen05_fence_after();
+                }
+                uint32_t const channel = static_cast<uint32_t>(step) * 16u;
+                int next_band = band == prefixes_ ? prefixes_ - 1 : band;
+                while (next_band > 0 && channel < p.ladder.ends[next_band - 1]) --next_band;
+                if (next_band != band) {
+                    band = next_band;
+                    uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
+                    if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
+                    tcgen05_fence_after();
+                    slot_address = tmem_base + slot * fwd_slot_columns;
+                    accumulate = 0;
+                    ++unit;
+                }
+                uint32_t const q_address = stages_base + stage * fwd_stage_bytes + sub * 32u;
+                umma_bf16(slot_address, umma_desc_k_major_sw128(q_address, 1024u),
+                          umma_desc_k_major_sw128(q_address + fwd_q_bytes, 1024u), idesc, accumulate);
+                accumulate = 1;
+                if (sub == 0u) {
+                    umma_commit(smem_u32(&tail->stage_empty[stage]));
+                    if (++stage == fwd_stages) stage = 0, phase ^= 1u;
+                }
+            }
+            umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
+            ++tile_local;
+        }
+    }
+}
+
+template <int prefixes_>
+__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, uint32_t tmem_base,
+                                              wait_context const& ctx, uint32_t warp, uint32_t lane) {
+    constexpr int columns = fwd_chunk<prefixes_>::columns;
+    constexpr int chunks_per_half = 32 / columns;
+    uint32_t const quadrant = warp % 4, half = warp / 4;
+    uint32_t const row_local = quadrant * 32 + lane;
+    uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16);
+    uint32_t const column_tiles = p.rows_c / fwd_cols;
+    uint32_t const quantities = 2 + 2 * prefixes_;
+    row_constants const constants{p.beta, p.bias, p.weight, 2.0f * p.beta * p.weight};
+    uint32_t tile_local = 0;
+
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
+        uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
+        uint32_t const row = strip * fwd_rows + row_local;
+        uint64_t const global_row = p.query_base + row;
+        float inv_q[prefixes_], row_beta[prefixes_], row_gain[prefixes_];
+#pragma unroll
+        for (int k = 0; k < prefixes_; ++k) {
+            inv_q[k] = p.q_inv[static_cast<size_t>(k) * p.rows_q + row];
+            row_beta[k] = p.beta * inv_q[k];
+            row_gain[k] = constants.two_beta_weight * inv_q[k];
+        }
+        float loss[prefixes_], coefficient[prefixes_], g = 0.0f, ga = 0.0f;
+#pragma unroll
+        for (int k = 0; k < prefixes_; ++k) loss[k] = 0.0f, coefficient[k] = 0.0f;
+
+        for (uint32_t t = 0; t < p.tiles_per_run; ++t, ++tile_local) {
+            uint32_t const column_tile = run * p.tiles_per_run + t;
+            uint32_t const column0 = column_tile * fwd_cols + half * 32;
+            // Is this a tile where every cell is a plain negative off the cosine floor?
+            uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
+            uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
+            bool special = first_column < first_row + fwd_rows + 1 && first_row < first_column + fwd_cols + 1;
+#pragma unroll
+            for (int k = 0; k < prefixes_; ++k)
+                special |= inv_q[k] * p.c_tile_max[static_cast<size_t>(k) * column_tiles + column_tile] >= 100.0f;
+            special = __any_sync(0xFFFFFFFFu, special);
+
+            if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u,
+                           ctx, site_fwd_tile_full, tile_local))
+                return;
+            tcgen05_fence_after();
+
+#pragma unroll 1
+            for (int chunk = 0; chunk < chunks_per_half; ++chunk) {
+                uint32_t const column = column0 + chunk * columns;
+                uint32_t d[prefixes_][columns];
+#pragma unroll
+                for (int k = 0; k < prefixes_; ++k) {
+                    uint32_t const slot = (tile_local * prefixes_ + (prefixes_ - 1 - k)) % fwd_slots;
+                    tmem_load_columns<columns>(lane_base + slot * fwd_slot_columns + half * 32 + chunk * columns, d[k]);
+                }
+                tmem_load_wait();
+                float prefix[columns];
+#pragma unroll
+                for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
+#pragma unroll
+                for (int k = 0; k < prefixes_; ++k) {
+                    float inv_c[columns];
+                    float4 const* source = reinterpret_cast<float4 const*>(p.c_inv + static_cast<size_t>(k) * p.rows_c + column);
+#pragma unroll
+                    for (int v = 0; v < columns / 4; ++v) {
+                        float4 const four = __ldg(source + v);
+                        inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
+                    }
+                    if (!special) {
+#pragma unroll
+                        for (int c = 0; c < columns; ++c) {
+                            prefix[c] += __uint_as_float(d[k][c]);
+                            d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], row_gain[k], p.bias, loss[k], g,
+                                                                ga, coefficient[k]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < columns; ++c) {
+                            prefix[c] += __uint_as_float(d[k][c]);
+                            d[k][c] = __float_as_uint(cell_general(prefix[c], inv_q[k], inv_c[c], constants, global_row,
+                                                                   p.candidate_base + column + c, p.spec_code, loss[k], g, ga,
+                                                                   coefficient[k]));
+                        }
+                    }
+                }
+                // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
+                float running[columns];
+#pragma unroll
+                for (int c = 0; c < columns; ++c) running[c] = 0.0f;
+#pragma unroll
+                for (int k = prefixes_ - 1; k >= 0; --k) {
+                    uint32_t packed[columns / 2];
+#pragma unroll
+                    for (int c = 0; c < columns; c += 2) {
+                        running[c] += __uint_as_float(d[k][c]);
+                        running[c + 1] += __uint_as_float(d[k][c + 1]);
+                        packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
+                    }
+                    uint4* destination = reinterpret_cast<uint4*>(
+                        p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
+#pragma unroll
+                    for (int v = 0; v < columns / 8; ++v)
+                        destination[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                }
+            }
+            // This warp is done with the tile's slots.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < prefixes_; ++k)
+                    mbar_arrive(smem_u32(&tail->slot_empty[(tile_local * prefixes_ + k) % fwd_slots]));
+            }
+        }
+        // One partial record per (run, half, row), weight applied here.
+        uint32_t const slot = run * 2 + half;
+        float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
+        record[0] = p.weight * g;
+        record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - p.bias * g);
+#pragma unroll
+        for (int k = 0; k < prefixes_; ++k) {
+            record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * loss[k];
+            record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] = coefficient[k];
+        }
+    }
+}
+
+__device__ __forceinline__ void pull_role(pull_request const& request, uint32_t thread_in_role) {
+    size_t const thread = static_cast<size_t>(blockIdx.x) * (fwd_pull_warps * 32) + thread_in_role;
+    size_t const threads = static_cast<size_t>(gridDim.x) * (fwd_pull_warps * 32);
+    for (int part = 0; part < 2; ++part) {
+        size_t const vectors = request.bytes[part] / 16;
+        if (vectors == 0) continue;
+        uint4 const* src = static_cast<uint4 const*>(request.src[part]);
+        uint4* dst = static_cast<uint4*>(request.dst[part]);
+        size_t index = thread;
+        for (; index + 3 * threads < vectors; index += 4 * threads) {
+            uint4 const a = src[index], b = src[index + threads], c = src[index + 2 * threads], d = src[index + 3 * threads];
+            dst[index] = a, dst[index + threads] = b, dst[index + 2 * threads] = c, dst[index + 3 * threads] = d;
+        }
+        for (; index < vectors; index += threads) dst[index] = src[index];
+    }
+}
+
+template <int prefixes_>
+__global__ void __launch_bounds__(fwd_threads, 1)
+    forward_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap c_map, const fwd_params p) {
+    extern __shared__ uint8_t raw_shared[];
+    uint32_t const raw_address = smem_u32(raw_shared);
+    uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
+    fwd_tail* tail = reinterpret_cast<fwd_tail*>(raw_shared + (stages_base - raw_address) + fwd_stages * fwd_stage_bytes);
+    uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        tail->abort_flag = status_poisoned(p.status) ? 1u : 0u;
+        for (uint32_t i = 0; i < fwd_stages; ++i) {
+            mbar_init(smem_u32(&tail->stage_full[i]), 1);
+            mbar_init(smem_u32(&tail->stage_empty[i]), 1);
+        }
+        for (uint32_t i = 0; i < fwd_slots; ++i) mbar_init(smem_u32(&tail->slot_empty[i]), fwd_epilogue_warps);
+        for (uint32_t i = 0; i < fwd_tile_barriers; ++i) mbar_init(smem_u32(&tail->tile_full[i]), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (tail->abort_flag != 0u) return; // a poisoned status block: nothing was allocated, every thread leaves
+    if (warp == fwd_mma_warp) {
+        tmem_alloc(smem_u32(&tail->tmem_base), fwd_tmem_columns);
+        tmem_relinquish();
+    }
+    if (warp == fwd_producer_warp && lane == 0) {
+        tma_prefetch_descriptor(&q_map);
+        tma_prefetch_descriptor(&c_map);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    uint32_t const tmem_base = tail->tmem_base;
+    wait_context const ctx{p.status, p.budget_ns, &tail->abort_flag};
+
+    if (warp < fwd_epilogue_warps) {
+        epilogue_role<prefixes_>(p, tail, tmem_base, ctx, warp, lane);
+    } else if (warp == fwd_producer_warp) {
+        if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx);
+    } else if (warp == fwd_mma_warp) {
+        if (lane == 0) mma_role<prefixes_>(p, stages_base, tail, tmem_base, ctx);
+    } else {
+        pull_role(p.pull, threadIdx.x - fwd_first_pull_warp * 32);
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tail->abort_flag != 0u) {
+        // Something gave up. Give copies and UMMAs that are still in flight a bounded time to land before the tensor
+        // memory goes back.
+        uint64_t const start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == fwd_mma_warp) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, fwd_tmem_columns);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------
+CUtensorMap make_map_2d(void const* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    CUtensorMap map;
+    cuuint64_t const dims[2] = {inner, outer};
+    cuuint64_t const strides[1] = {inner * 2};
+    cuuint32_t const box[2] = {box_inner, box_outer};
+    cuuint32_t const element_strides[2] = {1, 1};
+    SC_DRIVER(cuTensorMapEncodeTiled, &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return map;
+}
+
+template <int prefixes_>
+void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, fwd_params const& p, int blocks, cudaStream_t stream) {
+    require(cudaFuncSetAttribute(forward_kernel<prefixes_>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_shared_bytes),
+            "raising the forward kernel's shared memory");
+    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes, stream>>>(q_map, c_map, p);
+}
+
+} // namespace
+
+uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run) { return 2 * (rows_c / fwd_cols) / tiles_per_run; }
+uint32_t forward_quantities(uint32_t prefixes) { return 2 + 2 * prefixes; }
+
+uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors) {
+    uint32_t const strips = rows_q / fwd_rows, column_tiles = rows_c / fwd_cols;
+    uint32_t best = 1;
+    for (uint32_t t = 1; t <= 32 && column_tiles % t == 0; t *= 2)
+        if (static_cast<uint64_t>(strips) * (column_tiles / t) >= 6ull * static_cast<uint64_t>(multiprocessors)) best = t;
+    return best;
+}
+
+void launch_forward(forward_arguments const& a, cudaStream_t stream) {
+    if (a.rows_q % fwd_rows || a.rows_c % fwd_cols || a.hidden % fwd_depth)
+        throw std::runtime_error("forward: rows must be multiples of 128 (queries) and 64 (candidates), hidden of 64");
+    if (a.ladder.count < 1 || a.ladder.count > 8 || a.ladder.ends[a.ladder.count - 1] != a.hidden)
+        throw std::runtime_error("forward: the ladder's widest prefix must equal hidden");
+    for (uint32_t band = 0; band < a.ladder.count; ++band)
+        if (a.ladder.ends[band] % 16) throw std::runtime_error("forward: band edges must be multiples of 16");
+    uint32_t const column_tiles = a.rows_c / fwd_cols;
+    if (a.tiles_per_run == 0 || column_tiles % a.tiles_per_run)
+        throw std::runtime_error("forward: tiles_per_run must divide the number of candidate tiles");
+    if (a.pull.bytes[0] % 16 || a.pull.bytes[1] % 16) throw std::runtime_error("forward: pull sizes must be multiples of 16");
+
+    fwd_params p{};
+    p.q_inv = a.query_inverse_norms, p.c_inv = a.candidate_inverse_norms, p.c_tile_max = a.candidate_tile_max;
+    p.cube = static_cast<__nv_bfloat16*>(a.gradient_cube_bf16);
+    p.partials = a.partials, p.status = a.status;
+    p.rows_q = a.rows_q, p.rows_c = a.rows_c, p.hidden = a.hidden;
+    p.ladder.count = a.ladder.count;
+    for (int i = 0; i < 8; ++i) p.ladder.ends[i] = a.ladder.ends[i];
+    p.tiles_per_run = a.tiles_per_run;
+    p.runs_per_strip = column_tiles / a.tiles_per_run;
+    p.items = (a.rows_q / fwd_rows) * p.runs_per_strip;
+    p.beta = a.beta, p.bias = a.bias, p.weight = a.weight;
+    p.query_base = a.query_base, p.candidate_base = a.candidate_base, p.spec_code = a.spec_code;
+    p.budget_ns = a.budget_ns;
+    p.pull = a.pull;
+
+    CUtensorMap const q_map = make_map_2d(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
+    CUtensorMap const c_map = make_map_2d(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
+    int blocks = static_cast<int>(p.items < static_cast<uint32_t>(a.multiprocessors) ? p.items : a.multiprocessors);
+    if ((a.pull.bytes[0] | a.pull.bytes[1]) != 0 && blocks < a.multiprocessors / 2) blocks = a.multiprocessors / 2;
+    if (blocks < 1) blocks = 1;
+    switch (a.ladder.count) {
+    case 1: launch_instance<1>(q_map, c_map, p, blocks, stream); break;
+    case 2: launch_instance<2>(q_map, c_map, p, blocks, stream); break;
+    case 3: launch_instance<3>(q_map, c_map, p, blocks, stream); break;
+    case 4: launch_instance<4>(q_map, c_map, p, blocks, stream); break;
+    case 5: launch_instance<5>(q_map, c_map, p, blocks, stream); break;
+    case 6: launch_instance<6>(q_map, c_map, p, blocks, stream); break;
+    case 7: launch_instance<7>(q_map, c_map, p, blocks, stream); break;
+    default: launch_instance<8>(q_map, c_map, p, blocks, stream); break;
+    }
+    cudaError_t const error = cudaGetLastError();
+    if (error != cudaSuccess) throw std::runtime_error(std::string("forward launch failed: ") + cudaGetErrorString(error));
+    note_launch();
+}
+
+void preload_forward_kernels() {
+    cudaFuncAttributes attributes;
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<1>), "preload forward<1>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<2>), "preload forward<2>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<3>), "preload forward<3>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<4>), "preload forward<4>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<5>), "preload forward<5>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<6>), "preload forward<6>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<7>), "preload forward<7>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<8>), "preload forward<8>");
+}
+
+} // namespace sc

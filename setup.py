@@ -1,0 +1,31 @@
+"""In-tree build of the native extension: ``python setup.py build_ext --inplace``.
+
+Every CUDA source is compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``); passing the arch flags
+explicitly keeps torch's own architecture list out of the command line. The result lands beside the Python package as
+``scalingcontrasts_b200/_C*.so`` so that it travels with the source tree.
+"""
+import os
+
+from setuptools import setup
+from torch.utils.cpp_extension import BuildExtension, CUDAExtension
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join("scalingcontrasts_b200", "csrc")
+SOURCES = [os.path.join(CSRC, name) for name in (
+    "bindings.cpp", "domain.cpp", "oracle_cpu.cpp", "rail.cpp",
+    "collectives.cu", "loss_small.cu", "loss_fwd.cu", "loss_bwd.cu",
+)]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr"]
+
+setup(
+    name="scalingcontrasts_b200",
+    version="0.1.0",
+    packages=[],
+    ext_modules=[CUDAExtension(
+        name="scalingcontrasts_b200._C",
+        sources=SOURCES,
+        include_dirs=[os.path.join(ROOT, CSRC)],
+        extra_compile_args={"cxx": ["-O2", "-std=c++17"], "nvcc": NVCC_FLAGS},
+    )],
+    cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
+)
