@@ -22,8 +22,8 @@ from ..ladder import Matryoshka
 def prefix_inverse_norms(rows: torch.Tensor, ladder: Matryoshka, dtype=torch.float32) -> torch.Tensor:
     """``[K, R]`` inverse norms of every prefix; zero where the prefix is all zeros (scalingcontrasts.cuh:672-686)."""
     squares = rows.to(dtype).square()
-    running = torch.zeros(rows.shape[0], dtype=dtype)
-    out = torch.empty(ladder.count, rows.shape[0], dtype=dtype)
+    running = torch.zeros(rows.shape[0], dtype=dtype, device=rows.device)
+    out = torch.empty(ladder.count, rows.shape[0], dtype=dtype, device=rows.device)
     for band in range(ladder.count):
         running = running + squares[:, ladder.begin(band):ladder.end(band)].sum(dim=1)
         out[band] = torch.where(running > 0, running.rsqrt(), torch.zeros_like(running))
@@ -31,20 +31,26 @@ def prefix_inverse_norms(rows: torch.Tensor, ladder: Matryoshka, dtype=torch.flo
 
 
 class CpuStreamedLoss:
-    """One rank's streamed loss state on the CPU."""
+    """One rank's streamed loss state in plain torch operations (on the CPU by default; any torch device works, which
+    is how the device kernels' intermediates are checked in place)."""
 
     def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC,
-                 dtype: torch.dtype = torch.float32) -> None:
+                 dtype: torch.dtype = torch.float32, device="cpu", keep_cubes: bool = False) -> None:
         if ladder.hidden != hidden:
             raise ValueError(f"the widest prefix {ladder.hidden} must equal hidden {hidden}")
         self.rows, self.hidden, self.ladder, self.spec, self.dtype = rows, hidden, ladder, spec, dtype
+        self.device = torch.device(device)
         k = ladder.count
-        self.query_inverse_norms = torch.zeros(k, rows, dtype=dtype)
-        self.query_gradient = torch.zeros(rows, hidden, dtype=dtype)
-        self.row_loss = torch.zeros(k, rows, dtype=dtype)
-        self.row_bias_grad = torch.zeros(rows, dtype=dtype)
-        self.row_log_beta_grad = torch.zeros(rows, dtype=dtype)
-        self.self_coefficients = torch.zeros(k, rows, dtype=dtype)
+        options = dict(dtype=dtype, device=self.device)
+        self.query_inverse_norms = torch.zeros(k, rows, **options)
+        self.query_gradient = torch.zeros(rows, hidden, **options)
+        self.row_loss = torch.zeros(k, rows, **options)
+        self.row_bias_grad = torch.zeros(rows, **options)
+        self.row_log_beta_grad = torch.zeros(rows, **options)
+        self.self_coefficients = torch.zeros(k, rows, **options)
+        self.keep_cubes = keep_cubes
+        self.last_cubes = None  # [K, R, C] suffix-summed raw-dot gradients of the last score(), when kept
+        self.last_prefix_dots = None
         self._begun = False
 
     def bytes(self) -> int:
@@ -72,18 +78,21 @@ class CpuStreamedLoss:
         columns = c.shape[0]
         weight = 1.0 / float(live)
         candidate_inverse_norms = prefix_inverse_norms(candidates, self.ladder, dtype)
-        row_index = torch.arange(query_base, query_base + self.rows).unsqueeze(1)
-        column_index = torch.arange(candidate_base, candidate_base + columns).unsqueeze(0)
+        row_index = torch.arange(query_base, query_base + self.rows, device=self.device).unsqueeze(1)
+        column_index = torch.arange(candidate_base, candidate_base + columns, device=self.device).unsqueeze(0)
         own = row_index == column_index
-        z = torch.full((self.rows, columns), -1.0, dtype=dtype)
-        mask = torch.ones((self.rows, columns), dtype=dtype)
+        z = torch.full((self.rows, columns), -1.0, dtype=dtype, device=self.device)
+        mask = torch.ones((self.rows, columns), dtype=dtype, device=self.device)
+        if self.keep_cubes:
+            self.last_cubes = torch.zeros(self.ladder.count, self.rows, columns, dtype=dtype, device=self.device)
+            self.last_prefix_dots = torch.zeros(self.ladder.count, self.rows, columns, dtype=dtype, device=self.device)
         if self.spec.pairs:
             z = torch.where((row_index ^ 1) == column_index, torch.ones_like(z), z)
         if self.spec.diagonal == "own":
             z = torch.where(own, torch.ones_like(z), z)
         elif self.spec.diagonal == "skip":
             mask = torch.where(own, torch.zeros_like(mask), mask)
-        suffix = torch.zeros(self.rows, columns, dtype=dtype)
+        suffix = torch.zeros(self.rows, columns, dtype=dtype, device=self.device)
         for band in reversed(range(self.ladder.count)):
             end = self.ladder.end(band)
             dots = q[:, :end] @ c[:, :end].T
@@ -104,6 +113,9 @@ class CpuStreamedLoss:
                                    2.0 * beta * cell_grad * inverse_denominator)
             self.self_coefficients[band] += (raw_grad * dots).sum(dim=1)
             suffix = suffix + raw_grad
+            if self.keep_cubes:
+                self.last_cubes[band] = suffix
+                self.last_prefix_dots[band] = dots
             begin = self.ladder.begin(band)
             self.query_gradient[:, begin:end] += suffix @ c[:, begin:end]
 
@@ -114,16 +126,16 @@ class CpuStreamedLoss:
         if not self._begun:
             raise RuntimeError("finish() before begin()")
         q = queries.to(self.dtype)
-        fold = torch.zeros(self.rows, self.hidden, dtype=self.dtype)
+        fold = torch.zeros(self.rows, self.hidden, dtype=self.dtype, device=self.device)
         for band in range(self.ladder.count):
             term = self.self_coefficients[band] * self.query_inverse_norms[band].square()
             fold[:, :self.ladder.end(band)] += term[:, None]
         gradient = self.query_gradient - fold * q
         if gradient_out is None:
-            gradient_out = torch.empty(self.rows, self.hidden, dtype=queries.dtype)
+            gradient_out = torch.empty(self.rows, self.hidden, dtype=queries.dtype, device=self.device)
         gradient_out.copy_(gradient.to(gradient_out.dtype))
         if summands is None:
-            summands = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32)
+            summands = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32, device=self.device)
         summands.zero_()
         summands[0] = float(self.row_loss.sum())
         summands[1] = float(self.row_bias_grad.sum())

@@ -102,6 +102,7 @@ struct forward_arguments {
     ladder_host ladder;
     uint32_t tiles_per_run;
     float beta, bias, weight;
+    float const* scalars;            // optional device {beta, bias}; overrides the two floats above when set
     uint64_t query_base, candidate_base;
     uint32_t spec_code;
     uint64_t budget_ns;

@@ -181,7 +181,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("forward",
           [](uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t cube,
              uint64_t partials, uint64_t status, uint32_t rows_q, uint32_t rows_c, uint32_t hidden,
-             std::vector<uint32_t> const& ends, uint32_t tiles_per_run, float beta, float bias, float weight, uint64_t query_base,
+             std::vector<uint32_t> const& ends, uint32_t tiles_per_run, float beta, float bias, float weight, uint64_t scalars,
+             uint64_t query_base,
              uint64_t candidate_base, uint32_t spec_code, uint64_t budget_ns, uint64_t pull_src0, uint64_t pull_dst0,
              uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1, int sms, uint64_t stream) {
               sc::forward_arguments a{};
@@ -192,6 +193,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               a.status = pointer<uint32_t>(status);
               a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends);
               a.tiles_per_run = tiles_per_run, a.beta = beta, a.bias = bias, a.weight = weight;
+              a.scalars = pointer<float>(scalars);
               a.query_base = query_base, a.candidate_base = candidate_base, a.spec_code = spec_code, a.budget_ns = budget_ns;
               a.pull.src[0] = pointer<void>(pull_src0), a.pull.dst[0] = pointer<void>(pull_dst0), a.pull.bytes[0] = pull_bytes0;
               a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;

@@ -72,6 +72,7 @@ struct fwd_params {
     ladder_t ladder;
     uint32_t tiles_per_run, runs_per_strip, items;
     float beta, bias, weight;
+    float const* scalars; // optional device copy of {beta, bias}: learnable values never visit the host
     uint64_t query_base, candidate_base;
     uint32_t spec_code;
     uint64_t budget_ns;
@@ -224,7 +225,9 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
     uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16);
     uint32_t const column_tiles = p.rows_c / fwd_cols;
     uint32_t const quantities = 2 + 2 * prefixes_;
-    row_constants const constants{p.beta, p.bias, p.weight, 2.0f * p.beta * p.weight};
+    float const beta = p.scalars != nullptr ? __ldg(p.scalars) : p.beta;
+    float const bias = p.scalars != nullptr ? __ldg(p.scalars + 1) : p.bias;
+    row_constants const constants{beta, bias, p.weight, 2.0f * beta * p.weight};
     uint32_t tile_local = 0;
 
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
@@ -235,7 +238,7 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
 #pragma unroll
         for (int k = 0; k < prefixes_; ++k) {
             inv_q[k] = p.q_inv[static_cast<size_t>(k) * p.rows_q + row];
-            row_beta[k] = p.beta * inv_q[k];
+            row_beta[k] = beta * inv_q[k];
             row_gain[k] = constants.two_beta_weight * inv_q[k];
         }
         float loss[prefixes_], coefficient[prefixes_], g = 0.0f, ga = 0.0f;
@@ -285,7 +288,7 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
 #pragma unroll
                         for (int c = 0; c < columns; ++c) {
                             prefix[c] += __uint_as_float(d[k][c]);
-                            d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], row_gain[k], p.bias, loss[k], g,
+                            d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], row_gain[k], bias, loss[k], g,
                                                                 ga, coefficient[k]));
                         }
                     } else {
@@ -331,7 +334,7 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
         uint32_t const slot = run * 2 + half;
         float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
         record[0] = p.weight * g;
-        record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - p.bias * g);
+        record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
 #pragma unroll
         for (int k = 0; k < prefixes_; ++k) {
             record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * loss[k];
@@ -473,6 +476,7 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     p.runs_per_strip = column_tiles / a.tiles_per_run;
     p.items = (a.rows_q / fwd_rows) * p.runs_per_strip;
     p.beta = a.beta, p.bias = a.bias, p.weight = a.weight;
+    p.scalars = a.scalars;
     p.query_base = a.query_base, p.candidate_base = a.candidate_base, p.spec_code = a.spec_code;
     p.budget_ns = a.budget_ns;
     p.pull = a.pull;

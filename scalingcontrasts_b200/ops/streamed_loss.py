@@ -1,0 +1,233 @@
+"""The streamed, row-owned Matryoshka sigmoid loss on one B200: ``begin``, then ``score`` once per candidate block in
+any order, then ``finish``.
+
+A rank owns ``rows`` query rows. Each ``score`` runs, on the calling stream,
+
+1. (unless the caller supplies them) the candidates' prefix inverse norms and per-tile maxima,
+2. the forward tile kernel (tcgen05): segment dots of every band in tensor memory, sigmoid loss, per-band
+   suffix-summed gradient cube in bfloat16, per-row partial sums; optionally the same launch pulls the next block from
+   a peer's memory into local staging,
+3. the deterministic fold of the partials,
+4. a transpose of the candidates and the backward tile kernel (tcgen05) that folds the cube into the query gradient.
+
+``finish`` folds the L2-normalisation's self term, casts the gradient to bfloat16 and reduces the row summands into
+``summands`` (any device float32 span of ``SUMMAND_SLOTS`` values, a domain payload included):
+``[loss, d/d bias, d/d log(beta), 0, loss of prefix 0, ..., loss of prefix 7]``. Summands are this rank's share: sum
+them across ranks. The embedding gradient is final as computed (the owner applies a cell and its mirror), so no
+gradient crosses GPUs.
+
+Scratch memory is allocated once, in ``__init__``, and is independent of the number of blocks scored.
+
+Parity: ``streamed_loss_t`` (scalingcontrasts.cuh:1179-1324) and Mojo ``StreamedLoss`` (scalingcontrasts.mojo:1560-1781).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .._ext import native
+from ..config import LossSpec, REFERENCE_SPEC, SUMMAND_SLOTS
+from ..ladder import Matryoshka
+
+
+@dataclass
+class PullRequest:
+    """Up to two contiguous spans to copy (peer memory -> local memory) inside the next forward launch."""
+
+    src0: int = 0
+    dst0: int = 0
+    bytes0: int = 0
+    src1: int = 0
+    dst1: int = 0
+    bytes1: int = 0
+
+
+class BlockNorms:
+    """Inverse prefix norms ``[K, R]`` of a block followed by their per-64-row maxima ``[K, R/64]`` in one contiguous
+    float32 buffer, so that a block's norms travel with it as a single span."""
+
+    def __init__(self, prefixes: int, rows: int, storage: Optional[torch.Tensor] = None, device=None) -> None:
+        self.prefixes, self.rows = prefixes, rows
+        self.scalars = BlockNorms.scalars_for(prefixes, rows)
+        if storage is None:
+            storage = torch.empty(self.scalars, dtype=torch.float32, device=device)
+        if storage.numel() != self.scalars or storage.dtype != torch.float32:
+            raise ValueError("BlockNorms storage has the wrong size or dtype")
+        self.storage = storage
+        self.inverse = storage[:prefixes * rows].view(prefixes, rows)
+        self.tile_max = storage[prefixes * rows:prefixes * rows + prefixes * (rows // 64)].view(prefixes, rows // 64)
+
+    @staticmethod
+    def scalars_for(prefixes: int, rows: int) -> int:
+        """Scalars of the buffer, rounded up to whole 16-byte vectors so that the span can be pulled as one."""
+        return -(-(prefixes * rows + prefixes * (rows // 64)) // 4) * 4
+
+    @property
+    def nbytes(self) -> int:
+        return self.scalars * 4
+
+
+def _stream(stream) -> int:
+    return (torch.cuda.current_stream() if stream is None else stream).cuda_stream
+
+
+def compute_block_norms(rows: torch.Tensor, ladder: Matryoshka, norms: BlockNorms, copy_to: Optional[torch.Tensor] = None,
+                        stream=None) -> None:
+    """Fills ``norms`` for the bfloat16 block ``rows``; optionally copies the block to ``copy_to`` in the same pass
+    (used to publish a block into symmetric memory)."""
+    _check_block(rows)
+    copy_pointer = 0
+    if copy_to is not None:
+        if copy_to.shape != rows.shape or copy_to.dtype != torch.bfloat16 or not copy_to.is_contiguous():
+            raise ValueError("copy_to must match the block")
+        copy_pointer = copy_to.data_ptr()
+    native().prefix_norms(rows.data_ptr(), copy_pointer, norms.inverse.data_ptr(), norms.tile_max.data_ptr(),
+                          rows.shape[0], rows.shape[1], list(ladder.ends), _stream(stream))
+
+
+def _check_block(block: torch.Tensor) -> None:
+    if block.dtype != torch.bfloat16 or block.dim() != 2 or not block.is_contiguous() or not block.is_cuda:
+        raise ValueError("a block must be a contiguous CUDA bfloat16 matrix")
+    if block.data_ptr() % 16:
+        raise ValueError("a block must start on a 16-byte boundary")
+
+
+class StreamedLoss:
+    """One rank's streamed loss state on a GPU. See the module docstring for the contract."""
+
+    def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, device=None,
+                 candidate_rows: Optional[int] = None, budget_s: float = 2.0, backward_split: int = 0) -> None:
+        ladder.check_device_shape(rows, hidden)
+        self.rows, self.hidden, self.ladder, self.spec = rows, hidden, ladder, spec
+        self.candidate_rows = rows if candidate_rows is None else candidate_rows
+        if self.candidate_rows % 128:
+            raise ValueError("candidate blocks must hold a multiple of 128 rows")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.budget_ns = int(budget_s * 1e9)
+        properties = torch.cuda.get_device_properties(self.device)
+        self.multiprocessors = properties.multi_processor_count
+        k, ext = ladder.count, native()
+        self.tiles_per_run = int(ext.forward_choose_tiles_per_run(rows, self.candidate_rows, self.multiprocessors))
+        self.partial_slots = int(ext.forward_partial_slots(self.candidate_rows, self.tiles_per_run))
+        self.quantities = int(ext.forward_quantities(k))
+        if backward_split <= 0:
+            tiles = sum(-(-ladder.width(b) // 192) for b in range(k)) * (rows // 128)
+            backward_split = max(1, min(8, (2 * self.multiprocessors) // max(tiles, 1)))
+        self.backward_split = int(backward_split)
+        f32 = dict(dtype=torch.float32, device=self.device)
+        bf16 = dict(dtype=torch.bfloat16, device=self.device)
+        self.query_norms = BlockNorms(k, rows, device=self.device)
+        self.candidate_norms = BlockNorms(k, self.candidate_rows, device=self.device)
+        self.query_gradient = torch.zeros(rows, hidden, **f32)
+        self.row_accumulators = torch.zeros(self.quantities, rows, **f32)
+        self.partials = torch.empty(self.partial_slots, self.quantities, rows, **f32)
+        self.similarity_gradients = torch.empty(k, rows, self.candidate_rows, **bf16)
+        self.transposed_candidates = torch.empty(hidden, self.candidate_rows, **bf16)
+        self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self._begun = False
+        self._query_norms_view: Optional[BlockNorms] = None
+
+    # ------------------------------------------------------------------------------------------------------
+    def bytes(self) -> int:
+        """Bytes of scratch this object holds; does not grow with the number of blocks scored."""
+        tensors = (self.query_norms.storage, self.candidate_norms.storage, self.query_gradient, self.row_accumulators,
+                   self.partials, self.similarity_gradients, self.transposed_candidates, self.status)
+        return sum(t.numel() * t.element_size() for t in tensors)
+
+    def begin(self, queries: torch.Tensor, stream=None, query_norms: Optional[BlockNorms] = None) -> None:
+        """Clears the per-row accumulators and takes the queries' prefix norms (computed here unless supplied)."""
+        self._check_queries(queries)
+        with torch.cuda.stream(stream) if stream is not None else _NullContext():
+            self.query_gradient.zero_()
+            self.row_accumulators.zero_()
+        if query_norms is None:
+            compute_block_norms(queries, self.ladder, self.query_norms, stream=stream)
+            self._query_norms_view = self.query_norms
+        else:
+            self._query_norms_view = query_norms
+        self._begun = True
+
+    def score(self, queries: torch.Tensor, candidates: torch.Tensor, query_base: int, candidate_base: int, beta: float,
+              bias: float, live: int, stream=None, *, candidate_norms: Optional[BlockNorms] = None,
+              scalars: Optional[torch.Tensor] = None, pull_next: Optional[PullRequest] = None) -> None:
+        """Scores one candidate block (local memory) against this rank's rows.
+
+        ``scalars``, when given, is a device float32 ``[beta, bias]`` that overrides the two host floats, so learnable
+        values never visit the host. ``pull_next`` rides in the forward launch: the copy it names overlaps this block's
+        scoring."""
+        if not self._begun:
+            raise RuntimeError("score() before begin()")
+        self._check_queries(queries)
+        _check_block(candidates)
+        if tuple(candidates.shape) != (self.candidate_rows, self.hidden):
+            raise ValueError(f"candidates must be [{self.candidate_rows}, {self.hidden}]")
+        ext, s = native(), _stream(stream)
+        if candidate_norms is None:
+            compute_block_norms(candidates, self.ladder, self.candidate_norms, stream=stream)
+            candidate_norms = self.candidate_norms
+        pull = pull_next or PullRequest()
+        qn = self._query_norms_view
+        ext.forward(queries.data_ptr(), candidates.data_ptr(), qn.inverse.data_ptr(), candidate_norms.inverse.data_ptr(),
+                    candidate_norms.tile_max.data_ptr(), self.similarity_gradients.data_ptr(), self.partials.data_ptr(),
+                    self.status.data_ptr(), self.rows, self.candidate_rows, self.hidden, list(self.ladder.ends),
+                    self.tiles_per_run, float(beta), float(bias), 1.0 / float(live),
+                    0 if scalars is None else scalars.data_ptr(), int(query_base), int(candidate_base), self.spec.code(),
+                    self.budget_ns, pull.src0, pull.dst0, pull.bytes0, pull.src1, pull.dst1, pull.bytes1,
+                    self.multiprocessors, s)
+        ext.fold_partials(self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.rows, self.partial_slots,
+                          self.quantities, s)
+        ext.transpose(candidates.data_ptr(), self.transposed_candidates.data_ptr(), self.candidate_rows, self.hidden, s)
+        ext.backward(self.similarity_gradients.data_ptr(), self.transposed_candidates.data_ptr(),
+                     self.query_gradient.data_ptr(), self.status.data_ptr(), self.rows, self.candidate_rows, self.hidden,
+                     list(self.ladder.ends), self.backward_split, self.budget_ns, s)
+
+    def finish(self, queries: torch.Tensor, gradient_out: Optional[torch.Tensor] = None,
+               summands: Optional[torch.Tensor] = None, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        if not self._begun:
+            raise RuntimeError("finish() before begin()")
+        self._check_queries(queries)
+        if gradient_out is None:
+            gradient_out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        _check_block(gradient_out)
+        if summands is None:
+            summands = torch.empty(SUMMAND_SLOTS, dtype=torch.float32, device=self.device)
+        if summands.dtype != torch.float32 or summands.numel() < SUMMAND_SLOTS or not summands.is_contiguous():
+            raise ValueError(f"summands must be a contiguous float32 span of at least {SUMMAND_SLOTS} values")
+        ext, s = native(), _stream(stream)
+        qn = self._query_norms_view
+        ext.finalize(queries.data_ptr(), qn.inverse.data_ptr(), self.row_accumulators.data_ptr(),
+                     self.query_gradient.data_ptr(), gradient_out.data_ptr(), self.rows, self.hidden, list(self.ladder.ends), s)
+        ext.sum_summands(self.row_accumulators.data_ptr(), summands.data_ptr(), self.rows, self.ladder.count, s)
+        self._begun = False
+        return gradient_out, summands
+
+    def check(self) -> None:
+        """Raises if a tile kernel's bounded wait ran out (reads the status block: synchronises)."""
+        words = [int(v) & 0xFFFFFFFF for v in self.status.cpu().tolist()]
+        if words[0] != 0:
+            raise RuntimeError(f"streamed loss kernel gave up: code {words[0]} at site {words[1]} "
+                               f"(detail {words[2]}, parity {words[3]}, barrier {words[4]:#x}, block {words[5]}, "
+                               f"thread {words[6]})")
+
+    def _check_queries(self, queries: torch.Tensor) -> None:
+        _check_block(queries)
+        if tuple(queries.shape) != (self.rows, self.hidden):
+            raise ValueError(f"queries must be [{self.rows}, {self.hidden}], got {tuple(queries.shape)}")
+
+
+class _NullContext:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *args):
+        return False
+
+
+def keyed_embeddings_device(rows: int, hidden: int, salt: int, scale: float, device=None) -> torch.Tensor:
+    """The device twin of ``utils.keyed.keyed_embeddings`` (bit-identical values)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=device)
+    native().keyed_embeddings(out.data_ptr(), rows, hidden, int(salt), float(scale), _stream(None))
+    return out

@@ -1,0 +1,126 @@
+"""The intra-box data-parallel loss step: every GPU owns ``rows`` rows and scores them against every GPU's block.
+
+One step on a rank, all on one stream and without a host synchronisation:
+
+1. publish: one pass computes the block's prefix norms and copies the block into the rank's symmetric replica, so that
+   peers find embeddings and norms side by side;
+2. a domain barrier says "everyone's block is complete";
+3. ``begin``, then one ``score`` per peer in the staggered order ``(rank + p) mod S`` (so the eight GPUs never all pull
+   from the same peer at once); the forward launch that scores block ``p`` also pulls block ``p+1`` from its owner's
+   replica into one of two local staging buffers with plain peer loads, so the NVLink transfer overlaps the scoring;
+4. ``finish`` writes the rank's summands straight into the domain payload, and the all-reduce sums them across ranks;
+   its entry and exit rounds double as the fence that says "everyone has finished reading my block".
+
+``simulate`` plays one rank of a larger world on a single GPU by scoring the own block ``S`` times under shifted
+candidate bases (timing and memory only; block 0 holds the own copies).
+
+Parity: ``step_box`` (scalingcontrasts.cu:294-311), ``run_simulate`` (scalingcontrasts.cu:377-394); the staging pull
+replaces the reference's serial ``cudaMemcpyAsync`` (scalingcontrasts.cuh:1262-1265).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..config import LossSpec, REFERENCE_SPEC, SUMMAND_SLOTS
+from ..ladder import Matryoshka
+from ..ops.streamed_loss import BlockNorms, PullRequest, StreamedLoss, compute_block_norms
+
+
+class BoxLoss:
+    """One rank's engine for box-wide loss steps. ``domain`` may be None for a single, unconnected GPU."""
+
+    def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, domain=None,
+                 device=None, budget_s: float = 2.0) -> None:
+        self.rows, self.hidden, self.ladder, self.spec, self.domain = rows, hidden, ladder, spec, domain
+        self.device = domain.device if domain is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
+        self.loss = StreamedLoss(rows, hidden, ladder, spec, self.device, budget_s=budget_s)
+        k = ladder.count
+        block_bytes = rows * hidden * 2
+        if domain is not None:
+            if domain.payload_scalars < SUMMAND_SLOTS:
+                raise ValueError(f"the domain's payload must hold at least {SUMMAND_SLOTS} scalars")
+            self._embeddings_offset = domain.alloc(block_bytes)
+            self._norms_offset = domain.alloc(BlockNorms.scalars_for(k, rows) * 4)
+            self.embeddings = domain.tensor(self._embeddings_offset, (rows, hidden), torch.bfloat16)
+            norms_storage = domain.tensor(self._norms_offset, (BlockNorms.scalars_for(k, rows),), torch.float32)
+            self.summands = domain.payload()[:SUMMAND_SLOTS]
+            self.members, self.member = domain.members, domain.member
+        else:
+            self.embeddings = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device)
+            norms_storage = torch.empty(BlockNorms.scalars_for(k, rows), dtype=torch.float32, device=self.device)
+            self.summands = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32, device=self.device)
+            self.members, self.member = 1, 0
+        self.norms = BlockNorms(k, rows, norms_storage)
+        self.staged = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
+        self.staged_norms = [BlockNorms(k, rows, device=self.device) for _ in range(2)]
+        self.gradient = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device)
+
+    @staticmethod
+    def heap_bytes(rows: int, hidden: int, prefixes: int) -> int:
+        """Symmetric heap a ``BoxLoss`` takes from its domain."""
+        return rows * hidden * 2 + BlockNorms.scalars_for(prefixes, rows) * 4 + 1024
+
+    def bytes(self) -> int:
+        own = sum(t.numel() * t.element_size() for t in self.staged) + sum(n.nbytes for n in self.staged_norms)
+        return self.loss.bytes() + own + self.gradient.numel() * 2
+
+    def _pull_from(self, member: int, slot: int) -> PullRequest:
+        return PullRequest(self.domain.address(self._embeddings_offset, member), self.staged[slot].data_ptr(),
+                           self.rows * self.hidden * 2, self.domain.address(self._norms_offset, member),
+                           self.staged_norms[slot].storage.data_ptr(), self.staged_norms[slot].nbytes)
+
+    # ------------------------------------------------------------------------------------------------------
+    def step(self, queries: torch.Tensor, beta: float = 10.0, bias: float = -10.0, scalars: Optional[torch.Tensor] = None,
+             gradient_out: Optional[torch.Tensor] = None, stream=None, reduce: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Runs one step; returns ``(gradient [R,H] bf16, summands [SUMMAND_SLOTS] f32)``. With ``reduce`` the summands
+        are the world's sums on return (stream order)."""
+        members, member, rows = self.members, self.member, self.rows
+        compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
+        if self.domain is not None:
+            self.domain.barrier(stream)
+        self.loss.begin(self.embeddings, stream, query_norms=self.norms)
+        live = members * rows
+        for p in range(members):
+            peer = (member + p) % members
+            if p == 0:
+                candidates, norms = self.embeddings, self.norms
+            else:
+                candidates, norms = self.staged[(p - 1) % 2], self.staged_norms[(p - 1) % 2]
+            pull = self._pull_from((member + p + 1) % members, p % 2) if p + 1 < members else None
+            self.loss.score(self.embeddings, candidates, member * rows, peer * rows, beta, bias, live, stream,
+                            candidate_norms=norms, scalars=scalars, pull_next=pull)
+        gradient = self.gradient if gradient_out is None else gradient_out
+        self.loss.finish(self.embeddings, gradient, self.summands, stream)
+        if reduce and self.domain is not None:
+            self.domain.all_reduce(SUMMAND_SLOTS, stream)
+        return gradient, self.summands
+
+    def simulate(self, queries: torch.Tensor, world: int, beta: float = 10.0, bias: float = -10.0, stream=None,
+                 pull: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One rank of a ``world``-GPU step on this GPU alone: the own block stands in for every peer's."""
+        rows = self.rows
+        compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
+        self.loss.begin(self.embeddings, stream, query_norms=self.norms)
+        for block in range(world):
+            if block == 0 or not pull:
+                candidates, norms = self.embeddings, self.norms
+            else:
+                candidates, norms = self.staged[(block - 1) % 2], self.staged_norms[(block - 1) % 2]
+            request = None
+            if pull and block + 1 < world:
+                slot = block % 2
+                request = PullRequest(self.embeddings.data_ptr(), self.staged[slot].data_ptr(), rows * self.hidden * 2,
+                                      self.norms.storage.data_ptr(), self.staged_norms[slot].storage.data_ptr(),
+                                      self.staged_norms[slot].nbytes)
+            self.loss.score(self.embeddings, candidates, 0, block * rows, beta, bias, world * rows, stream,
+                            candidate_norms=norms, pull_next=request)
+        self.loss.finish(self.embeddings, self.gradient, self.summands, stream)
+        return self.gradient, self.summands
+
+    def check(self) -> None:
+        self.loss.check()
+        if self.domain is not None:
+            self.domain.check()

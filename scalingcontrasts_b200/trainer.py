@@ -1,0 +1,150 @@
+"""``ContrastiveTrainer``: the headline training step as one public call.
+
+A step is: projector forward on a batch of rows, the box-wide Matryoshka sigmoid loss (streamed over every GPU's
+block), backward through the projector with the parameter gradients all-reduced on a side stream while backward still
+runs, and the optimizer update. Batches come from pinned host memory: ``feed`` starts the host-to-device copy of a batch
+on a copy stream (so the copy of batch t+1 hides under step t), ``step`` consumes the oldest fed batch and starts the
+device-to-host copy of its loss into pinned memory.
+
+The reference benchmarks a loss step only (scalingcontrasts.cu:294-311); a model, an optimizer and checkpoints are what
+a training framework adds around it.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Deque, Dict, Optional, Tuple
+
+import torch
+
+from .config import LossSpec, REFERENCE_SPEC
+from .ladder import Matryoshka
+from .models.loss import MatryoshkaSigmoidLoss
+from .models.projector import Projector
+from .parallel.reducer import GradientReducer
+
+
+class ContrastiveTrainer:
+    def __init__(self, rows: int, in_features: int = 1024, mid_features: int = 3072, hidden: int = 768, prefixes: int = 5,
+                 spec: LossSpec = REFERENCE_SPEC, lr: float = 1e-4, weight_decay: float = 0.0, group=None, device=None,
+                 seed: int = 0, multicast: Optional[bool] = None, optimizer: str = "adamw") -> None:
+        from .parallel.box import BoxLoss
+        from .parallel.domain import Domain
+
+        self.rows, self.in_features, self.hidden = rows, in_features, hidden
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.ladder = Matryoshka.halvings(hidden, prefixes)
+        self.projector = Projector(in_features, mid_features, hidden, torch.bfloat16, self.device, seed)
+        heap = BoxLoss.heap_bytes(rows, hidden, prefixes) + GradientReducer.heap_bytes(self.projector.parameters())
+        self.domain = Domain.create(payload_scalars=16, heap_bytes=heap, group=group, device=self.device, multicast=multicast)
+        self.world, self.rank = self.domain.members, self.domain.member
+        self.loss = MatryoshkaSigmoidLoss(rows, hidden, prefixes, self.ladder, spec, self.domain, group, self.device)
+        # Every rank's loss is the world's sum and row gradients are final, so parameter gradients are summed.
+        self.reducer = GradientReducer(self.projector.parameters(), self.domain, scale=1.0)
+        parameters = list(self.projector.parameters()) + list(self.loss.parameters())
+        if optimizer == "adamw":
+            self.optimizer = torch.optim.AdamW(parameters, lr=lr, weight_decay=weight_decay, fused=True)
+        elif optimizer == "sgd":
+            self.optimizer = torch.optim.SGD(parameters, lr=lr, momentum=0.9)
+        else:
+            raise ValueError("optimizer must be adamw or sgd")
+        self.steps_done = 0
+        self._copy_stream = torch.cuda.Stream(device=self.device)
+        self._slots = [torch.empty(rows, in_features, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
+        self._slot_free = [torch.cuda.Event() for _ in range(2)]
+        self._fed: Deque[Tuple[int, torch.cuda.Event]] = deque()
+        self._next_slot = 0
+        self._loss_host = torch.zeros(2, 16, dtype=torch.float32).pin_memory()
+        self._loss_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._loss_pending: Deque[int] = deque()
+        for event in self._slot_free:
+            event.record()
+
+    # -- data path --------------------------------------------------------------------------------------------
+    def feed(self, batch: torch.Tensor) -> None:
+        """Starts the host-to-device copy of one batch (pinned ``[rows, in_features]`` bfloat16) on the copy stream."""
+        if batch.device.type != "cpu" or tuple(batch.shape) != (self.rows, self.in_features) or batch.dtype != torch.bfloat16:
+            raise ValueError(f"a batch is a host bfloat16 tensor of shape [{self.rows}, {self.in_features}]")
+        if len(self._fed) >= 2:
+            raise RuntimeError("at most two batches may be in flight; call step() before feeding a third")
+        slot = self._next_slot
+        self._next_slot ^= 1
+        self._copy_stream.wait_event(self._slot_free[slot])
+        with torch.cuda.stream(self._copy_stream):
+            self._slots[slot].copy_(batch, non_blocking=True)
+            landed = torch.cuda.Event()
+            landed.record(self._copy_stream)
+        self._fed.append((slot, landed))
+
+    def step(self, batch: Optional[torch.Tensor] = None) -> Optional[float]:
+        """Runs one training step on the oldest fed batch (feeding ``batch`` first when given). Returns the loss of the
+        previous step, whose device-to-host copy has had a whole step to land, or None on the first call."""
+        if batch is not None:
+            self.feed(batch)
+        if not self._fed:
+            raise RuntimeError("step() without a fed batch")
+        slot, landed = self._fed.popleft()
+        torch.cuda.current_stream().wait_event(landed)
+        loss = self.step_on_device(self._slots[slot])
+        self._slot_free[slot].record()
+        previous = self._collect_loss()
+        index = self.steps_done % 2
+        self._loss_host[index, :12].copy_(self.loss.last_summands, non_blocking=True)
+        self._loss_events[index].record()
+        self._loss_pending.append(index)
+        return previous
+
+    def step_on_device(self, x: torch.Tensor) -> torch.Tensor:
+        """One step on a batch that already lives on the device; returns the loss as a device scalar."""
+        self.optimizer.zero_grad(set_to_none=True)
+        embeddings = self.projector(x)
+        loss = self.loss(embeddings)
+        loss.backward()
+        self.reducer.wait()
+        self.optimizer.step()
+        self.steps_done += 1
+        return loss
+
+    def _collect_loss(self) -> Optional[float]:
+        if not self._loss_pending:
+            return None
+        index = self._loss_pending.popleft()
+        self._loss_events[index].synchronize()
+        return float(self._loss_host[index, 0])
+
+    def last_loss(self) -> Optional[float]:
+        """The newest loss (synchronises on its copy)."""
+        value = None
+        while self._loss_pending:
+            value = self._collect_loss()
+        return value
+
+    # -- accounting -------------------------------------------------------------------------------------------
+    def cells_per_step(self) -> int:
+        return self.loss.cells_per_step(self.world)
+
+    def h2d_bytes_per_step(self) -> int:
+        return self.rows * self.in_features * 2
+
+    def d2h_bytes_per_step(self) -> int:
+        return 12 * 4
+
+    # -- checkpoints ------------------------------------------------------------------------------------------
+    def state_dict(self) -> Dict[str, object]:
+        return {"projector": self.projector.state_dict(), "loss": self.loss.state_dict(),
+                "optimizer": self.optimizer.state_dict(), "step": self.steps_done,
+                "ladder": list(self.ladder.ends)}
+
+    def load_state_dict(self, state: Dict[str, object]) -> None:
+        self.projector.load_state_dict(state["projector"])
+        self.loss.load_state_dict(state["loss"])
+        self.optimizer.load_state_dict(state["optimizer"])
+        self.steps_done = int(state["step"])
+
+    def check(self) -> None:
+        self.loss.engine.check()
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self.reducer.remove()
+        self.domain.close()
+

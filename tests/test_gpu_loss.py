@@ -1,0 +1,151 @@
+"""Device kernels of the streamed loss against plain float32 / float64 torch statements of the same operations."""
+import pytest
+import torch
+
+from scalingcontrasts_b200 import LossSpec, Matryoshka
+from scalingcontrasts_b200.cpu import CpuStreamedLoss, oracle, relative_l2
+from scalingcontrasts_b200.utils.keyed import keyed_embeddings, normal_embeddings
+
+pytestmark = pytest.mark.gpu
+
+
+def _loss(rows, hidden, ladder, spec=LossSpec("self")):
+    from scalingcontrasts_b200.ops.streamed_loss import StreamedLoss
+
+    return StreamedLoss(rows, hidden, ladder, spec, "cuda")
+
+
+def _float32_matmul_exact():
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+
+def test_prefix_norms_transpose_and_keyed_generator(ext):
+    from scalingcontrasts_b200.cpu.streamed import prefix_inverse_norms
+    from scalingcontrasts_b200.ops.streamed_loss import BlockNorms, compute_block_norms, keyed_embeddings_device
+
+    ladder = Matryoshka.halvings(768, 5)
+    block = keyed_embeddings_device(256, 768, salt=3, scale=1.0)
+    assert torch.equal(block.cpu(), keyed_embeddings(256, 768, 3, 1.0))
+    norms = BlockNorms(5, 256, device="cuda")
+    copy = torch.empty_like(block)
+    compute_block_norms(block, ladder, norms, copy_to=copy)
+    expected = prefix_inverse_norms(block, ladder)
+    assert torch.equal(copy, block)
+    assert torch.allclose(norms.inverse, expected, rtol=2e-6)
+    assert torch.allclose(norms.tile_max, expected.view(5, 4, 64).amax(dim=2), rtol=2e-6)
+    out = torch.empty(768, 256, dtype=torch.bfloat16, device="cuda")
+    ext.transpose(block.data_ptr(), out.data_ptr(), 256, 768, torch.cuda.current_stream().cuda_stream)
+    assert torch.equal(out, block.T.contiguous())
+
+
+@pytest.mark.parametrize("rows,hidden,prefixes", [(128, 64, 1), (128, 256, 3), (256, 768, 5), (128, 512, 8)])
+def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefixes):
+    """The forward kernel's per-band gradient cubes and the backward kernel's fold, each checked on its own."""
+    _float32_matmul_exact()
+    ladder = Matryoshka.halvings(hidden, prefixes)
+    queries = normal_embeddings(rows, hidden, seed=1, rank=0).cuda()
+    candidates = normal_embeddings(rows, hidden, seed=1, rank=1).cuda()
+    loss = _loss(rows, hidden, ladder)
+    loss.begin(queries)
+    loss.score(queries, candidates, 0, rows, 10.0, -10.0, 2 * rows)
+    torch.cuda.synchronize()
+    loss.check()
+    reference = CpuStreamedLoss(rows, hidden, ladder, LossSpec("self"), torch.float32, "cuda", keep_cubes=True)
+    reference.begin(queries)
+    reference.score(queries, candidates, 0, rows, 10.0, -10.0, 2 * rows)
+    cube = loss.similarity_gradients.float()
+    for band in range(prefixes):
+        assert relative_l2(cube[band], reference.last_cubes[band]) < 6e-3, f"cube of band {band}"
+    # backward alone: fold the kernel's own bfloat16 cube with a float32 matmul and compare
+    expected = torch.zeros(rows, hidden, device="cuda")
+    for band in range(prefixes):
+        begin, end = ladder.begin(band), ladder.end(band)
+        expected[:, begin:end] = cube[band] @ candidates.float()[:, begin:end]
+    assert relative_l2(loss.query_gradient, expected) < 1e-5
+    # row accumulators: bias-grad, log-beta-grad, prefix losses, coefficients
+    accumulators = loss.row_accumulators
+    assert torch.allclose(accumulators[0], reference.row_bias_grad, rtol=2e-4, atol=1e-9)
+    assert torch.allclose(accumulators[2:2 + prefixes], reference.row_loss, rtol=2e-5, atol=1e-9)
+    assert relative_l2(accumulators[2 + prefixes:], reference.self_coefficients) < 2e-4
+
+
+@pytest.mark.parametrize("spec", [LossSpec("self"), LossSpec("pairs"), LossSpec("pairs", "skip")],
+                         ids=lambda s: f"{s.positives}-{s.diagonal}")
+@pytest.mark.parametrize("rows,hidden,prefixes,kind", [(128, 256, 3, "normal"), (128, 768, 5, "normal"), (256, 768, 5, "keyed")])
+def test_world_of_two_blocks_against_the_float64_oracle(spec, rows, hidden, prefixes, kind):
+    """One GPU plays both ranks of a two-rank world in turn; loss, per-prefix losses, gradients and the two scalar
+    gradients are compared with the float64 evaluation of the whole world."""
+    ladder = Matryoshka.halvings(hidden, prefixes)
+    if kind == "normal":
+        blocks = [normal_embeddings(rows, hidden, seed=1, rank=r).cuda() for r in range(2)]
+    else:
+        blocks = [keyed_embeddings(rows, hidden, r, 1.0).cuda() for r in range(2)]
+    expected = oracle(torch.cat(blocks).cpu(), ladder, 10.0, -10.0, spec)
+    loss = _loss(rows, hidden, ladder, spec)
+    total = torch.zeros(12, dtype=torch.float64)
+    gradients = []
+    for rank in range(2):
+        loss.begin(blocks[rank])
+        for peer in (rank, 1 - rank):
+            loss.score(blocks[rank], blocks[peer], rank * rows, peer * rows, 10.0, -10.0, 2 * rows)
+        gradient, summands = loss.finish(blocks[rank])
+        torch.cuda.synchronize()
+        loss.check()
+        gradients.append(gradient.float().cpu())
+        total += summands.double().cpu()
+    assert float(total[0]) == pytest.approx(expected.loss, rel=2e-6)
+    assert torch.allclose(total[4:4 + prefixes], expected.band_losses, rtol=2e-6)
+    assert relative_l2(torch.cat(gradients), expected.gradient) < 4e-3
+    assert float(total[1]) == pytest.approx(expected.bias_grad, rel=1e-4)
+    assert float(total[2]) == pytest.approx(expected.log_beta_grad, rel=1e-3, abs=1e-6)
+
+
+def test_block_order_invariance_and_bitwise_repeat():
+    ladder = Matryoshka.halvings(256, 3)
+    blocks = [normal_embeddings(128, 256, seed=5, rank=r).cuda() for r in range(3)]
+    loss = _loss(128, 256, ladder)
+    results = []
+    for order in ((0, 1, 2), (2, 1, 0), (0, 1, 2)):
+        loss.begin(blocks[0])
+        for peer in order:
+            loss.score(blocks[0], blocks[peer], 0, peer * 128, 10.0, -10.0, 3 * 128)
+        gradient, summands = loss.finish(blocks[0])
+        torch.cuda.synchronize()
+        results.append((gradient.clone(), summands.clone()))
+    assert torch.equal(results[0][0], results[2][0]) and torch.equal(results[0][1], results[2][1])  # bit for bit
+    assert relative_l2(results[1][0].float(), results[0][0].float()) < 2e-3
+    assert torch.allclose(results[1][1], results[0][1], rtol=1e-5)
+
+
+@pytest.mark.parametrize("hidden,prefixes", [(64, 1), (256, 3)])
+def test_collinear_rows_have_exactly_zero_gradient(hidden, prefixes):
+    ladder = Matryoshka.halvings(hidden, prefixes)
+    rows = torch.zeros(128, hidden, dtype=torch.float32)
+    for i in range(128):
+        rows[i, 0] = [1.0, 1.0 / 16, 1.0 / 256, 0.0][i % 4]
+    block = rows.to(torch.bfloat16).cuda()
+    loss = _loss(128, hidden, ladder)
+    loss.begin(block)
+    loss.score(block, block, 0, 0, 10.0, -10.0, 128)
+    gradient, _ = loss.finish(block)
+    torch.cuda.synchronize()
+    loss.check()
+    assert torch.count_nonzero(gradient) == 0
+
+
+def test_scratch_does_not_grow_and_device_scalars_override():
+    ladder = Matryoshka.halvings(256, 3)
+    block = normal_embeddings(128, 256, seed=7).cuda()
+    loss = _loss(128, 256, ladder)
+    before = loss.bytes()
+    scalars = torch.tensor([10.0, -10.0], device="cuda")
+    outputs = []
+    for use_scalars in (False, True):
+        loss.begin(block)
+        for peer in range(4):
+            loss.score(block, block, 0, peer * 128, 1.0 if use_scalars else 10.0, 0.0 if use_scalars else -10.0, 4 * 128,
+                       scalars=scalars if use_scalars else None)
+        outputs.append(tuple(t.clone() for t in loss.finish(block)))
+    torch.cuda.synchronize()
+    assert loss.bytes() == before
+    assert torch.equal(outputs[0][0], outputs[1][0]) and torch.equal(outputs[0][1], outputs[1][1])

@@ -1,0 +1,41 @@
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_training_steps_reduce_the_loss_and_checkpoints_resume_bitwise(tmp_path):
+    from scalingcontrasts_b200.trainer import ContrastiveTrainer
+
+    def make():
+        return ContrastiveTrainer(rows=256, in_features=128, mid_features=256, hidden=256, prefixes=3, lr=1e-3, device="cuda", seed=3)
+
+    generator = torch.Generator().manual_seed(0)
+    batches = [torch.randn(256, 128, generator=generator).to(torch.bfloat16).pin_memory() for _ in range(4)]
+    trainer = make()
+    losses = []
+    for step in range(24):
+        trainer.step(batches[step % 4])
+        losses.append(trainer.last_loss())
+    trainer.check()
+    assert all(value == value for value in losses)
+    assert sum(losses[-4:]) < sum(losses[:4])
+    path = tmp_path / "checkpoint.pt"
+    torch.save(trainer.state_dict(), path)
+    trainer.step(batches[0])
+    expected = trainer.last_loss()
+    trainer.close()
+    resumed = make()
+    resumed.load_state_dict(torch.load(path, weights_only=False))
+    assert resumed.steps_done == 24
+    resumed.step(batches[0])
+    assert resumed.last_loss() == expected
+    state = resumed.loss.state_dict()
+    assert set(state) == {"logit_scale", "logit_bias"} and state["logit_scale"].dim() == 0
+    resumed.close()
+
+
+def test_smoke_entry_point():
+    import __graft_entry__
+
+    __graft_entry__.smoke()
