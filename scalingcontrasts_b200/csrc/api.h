@@ -95,7 +95,7 @@ struct forward_arguments {
     float const* query_inverse_norms;     // [K, rows_q]
     float const* candidate_inverse_norms; // [K, rows_c]
     float const* candidate_tile_max;      // [K, rows_c / 64]
-    void* gradient_cube_bf16;        // [K, rows_q, rows_c]
+    void* gradient_cube_bf16;        // [K, rows_q, rows_c], WITHOUT the factor 2 / live (the backward launch applies it)
     float* partials;                 // [slots, quantities, rows_q]
     uint32_t* status;
     uint32_t rows_q, rows_c, hidden;
@@ -123,6 +123,7 @@ struct backward_arguments {
     uint32_t rows_q, rows_c, hidden;
     ladder_host ladder;
     uint32_t split;                     // candidate-range splits (1: deterministic read-modify-write)
+    float scale;                        // multiplies every product before accumulation (the loss passes 2 / live)
     uint64_t budget_ns;
 };
 void launch_backward(backward_arguments const& arguments, cudaStream_t stream);

@@ -201,12 +201,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               sc::launch_forward(a, stream_of(stream));
           });
     m.def("backward", [](uint64_t cube, uint64_t transposed, uint64_t query_gradient, uint64_t status, uint32_t rows_q,
-                         uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, uint64_t budget_ns,
-                         uint64_t stream) {
+                         uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, float scale,
+                         uint64_t budget_ns, uint64_t stream) {
         sc::backward_arguments a{};
         a.gradient_cube_bf16 = pointer<void>(cube), a.transposed_candidates = pointer<void>(transposed);
         a.query_gradient = pointer<float>(query_gradient), a.status = pointer<uint32_t>(status);
-        a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends), a.split = split;
+        a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends), a.split = split, a.scale = scale;
         a.budget_ns = budget_ns;
         sc::launch_backward(a, stream_of(stream));
     });

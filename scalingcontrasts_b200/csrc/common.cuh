@@ -247,6 +247,18 @@ __device__ __forceinline__ float log1p_unit(float x) {
     p = fmaf(p, x, SC_LOG1P_C0);
     return p * x;
 }
+// The polynomial alone: log1p(x) = log1p_ratio(x) * x, for callers that fold the product into an accumulation.
+__device__ __forceinline__ float log1p_ratio(float x) {
+    float p = SC_LOG1P_C8;
+    p = fmaf(p, x, SC_LOG1P_C7);
+    p = fmaf(p, x, SC_LOG1P_C6);
+    p = fmaf(p, x, SC_LOG1P_C5);
+    p = fmaf(p, x, SC_LOG1P_C4);
+    p = fmaf(p, x, SC_LOG1P_C3);
+    p = fmaf(p, x, SC_LOG1P_C2);
+    p = fmaf(p, x, SC_LOG1P_C1);
+    return fmaf(p, x, SC_LOG1P_C0);
+}
 
 // Matryoshka ladder by value, the form kernels take (ascending ends, zero padded).
 struct ladder_t {

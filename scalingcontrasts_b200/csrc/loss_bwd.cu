@@ -51,6 +51,7 @@ struct bwd_params {
     uint32_t* status;
     uint32_t rows_q, rows_c, hidden;
     uint32_t tile_count, split;
+    float scale; // applied to every product before it is added: the loss's 2/N (mirror cell and weight)
     uint64_t budget_ns;
     bwd_tile tiles[bwd_max_tiles];
 };
@@ -148,15 +149,15 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                     for (int v = 0; v < 4; ++v) {
                         float4* address = reinterpret_cast<float4*>(destination + column) + v;
                         float4 current = *address;
-                        current.x += __uint_as_float(values[4 * v]);
-                        current.y += __uint_as_float(values[4 * v + 1]);
-                        current.z += __uint_as_float(values[4 * v + 2]);
-                        current.w += __uint_as_float(values[4 * v + 3]);
+                        current.x = fmaf(p.scale, __uint_as_float(values[4 * v]), current.x);
+                        current.y = fmaf(p.scale, __uint_as_float(values[4 * v + 1]), current.y);
+                        current.z = fmaf(p.scale, __uint_as_float(values[4 * v + 2]), current.z);
+                        current.w = fmaf(p.scale, __uint_as_float(values[4 * v + 3]), current.w);
                         *address = current;
                     }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) atomicAdd(destination + column + c, __uint_as_float(values[c]));
+                    for (int c = 0; c < 16; ++c) atomicAdd(destination + column + c, p.scale * __uint_as_float(values[c]));
                 }
             }
         }
@@ -193,7 +194,7 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     bwd_params p{};
     p.query_gradient = a.query_gradient, p.status = a.status;
     p.rows_q = a.rows_q, p.rows_c = a.rows_c, p.hidden = a.hidden;
-    p.split = a.split, p.budget_ns = a.budget_ns;
+    p.split = a.split, p.budget_ns = a.budget_ns, p.scale = a.scale;
     uint32_t begin = 0;
     for (uint32_t band = 0; band < a.ladder.count; ++band) {
         uint32_t const end = a.ladder.ends[band];

@@ -59,7 +59,8 @@ struct fwd_tail {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-constexpr uint32_t fwd_shared_bytes = 1024 + fwd_stages * fwd_stage_bytes + sizeof(fwd_tail);
+constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
+constexpr uint32_t fwd_shared_bytes = 1024 + fwd_stages * fwd_stage_bytes + fwd_tail_bytes + 8 * 2 * (8 * 32 + 8) * 4;
 
 struct fwd_params {
     float const* q_inv;
@@ -83,21 +84,23 @@ struct fwd_params {
 // Accumulators are kept without the 1/N weight: `g` sums -mask*z*(1-sigmoid(s)), `ga` sums that times (logit+bias),
 // `loss` sums mask*softplus(-s); the weight is applied once when the partial record is written.
 struct row_constants {
-    float beta, bias, weight, two_beta_weight;
+    float beta, bias, weight, raw_scale;
 };
 
-// A negative cell whose cosine is off the floor: z = -1, s = -(logit + bias).
-__device__ __forceinline__ float cell_fast(float prefix_dot, float inv_c, float row_beta, float row_gain, float bias,
-                                           float& loss, float& g, float& ga, float& coefficient) {
-    float const t = prefix_dot * inv_c;
-    float const a = fmaf(t, row_beta, bias);             // logit + bias
+// A negative cell whose cosine is off the floor: z = -1, s = -(logit + bias). Returns the gradient with respect to the
+// raw dot product WITHOUT the factor 2/N (mirror cell and weight), which the backward kernel applies once per element.
+__device__ __forceinline__ float cell_fast(float prefix_dot, float inv_c, float row_beta, float bias, float& loss, float& g,
+                                           float& ga, float& coefficient) {
+    float const scale = inv_c * row_beta;                 // beta / (|q| |c|)
+    float const a = fmaf(prefix_dot, scale, bias);        // logit + bias
     float const e = fast_ex2(-fabsf(a) * log2_e);         // exp(-|a|)
     float const r = fast_rcp(1.0f + e);
     float const complement = (a >= 0.0f ? 1.0f : e) * r;  // 1 - sigmoid(s) = sigmoid(a)
-    loss += fmaxf(a, 0.0f) + log1p_unit(e);
+    loss += fmaxf(a, 0.0f);
+    loss = fmaf(log1p_ratio(e), e, loss);
     g += complement;
     ga = fmaf(complement, a, ga);
-    float const raw = complement * inv_c * row_gain;      // d loss / d raw dot, mirror cell included
+    float const raw = complement * scale;
     coefficient = fmaf(raw, prefix_dot, coefficient);
     return raw;
 }
@@ -127,7 +130,7 @@ __device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, flo
     loss += mask * (fmaxf(-s, 0.0f) + log1p_unit(d));
     g += cell;
     ga = fmaf(cell, a, ga);
-    float const raw = (own || floored) ? 0.0f : cell * inverse_denominator * k.two_beta_weight;
+    float const raw = (own || floored) ? 0.0f : cell * inverse_denominator * k.raw_scale;
     coefficient = fmaf(raw, prefix_dot, coefficient);
     return raw;
 }
@@ -215,8 +218,24 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     }
 }
 
+// Position of a CTA in its fixed walk over (work item, tile of the run).
+struct tile_cursor {
+    uint32_t item, t;
+    __device__ __forceinline__ bool valid(fwd_params const& p) const { return item < p.items; }
+    __device__ __forceinline__ tile_cursor next(fwd_params const& p) const {
+        return t + 1 < p.tiles_per_run ? tile_cursor{item, t + 1} : tile_cursor{item + gridDim.x, 0};
+    }
+    __device__ __forceinline__ uint32_t column_tile(fwd_params const& p) const {
+        return (item % p.runs_per_strip) * p.tiles_per_run + t;
+    }
+};
+
+// Per-warp staging of a tile's candidate norms: [2 buffers][prefixes][32 columns] inverse norms, then [2][8] tile maxima.
+constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * 32 + 8);
+constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
+
 template <int prefixes_>
-__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, uint32_t tmem_base,
+__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, float* norm_staging, uint32_t tmem_base,
                                               wait_context const& ctx, uint32_t warp, uint32_t lane) {
     constexpr int columns = fwd_chunk<prefixes_>::columns;
     constexpr int chunks_per_half = 32 / columns;
@@ -227,119 +246,150 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
     uint32_t const quantities = 2 + 2 * prefixes_;
     float const beta = p.scalars != nullptr ? __ldg(p.scalars) : p.beta;
     float const bias = p.scalars != nullptr ? __ldg(p.scalars + 1) : p.bias;
-    row_constants const constants{beta, bias, p.weight, 2.0f * beta * p.weight};
-    uint32_t tile_local = 0;
+    row_constants const constants{beta, bias, p.weight, beta};
+    float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][prefixes_][32]
+    float* const staged_max = staged_norms + 2 * 8 * 32;                        // [2][8]
+    uint32_t tile_local = 0, buffer = 0;
 
-    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
-        uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
-        uint32_t const row = strip * fwd_rows + row_local;
-        uint64_t const global_row = p.query_base + row;
-        float inv_q[prefixes_], row_beta[prefixes_], row_gain[prefixes_];
+    tile_cursor cursor{blockIdx.x, 0};
+    if (!cursor.valid(p)) return;
+    // Norms of a tile's candidates are fetched one tile ahead into registers and parked in this warp's shared-memory
+    // buffer, so the cell loop reads them with broadcast shared loads instead of waiting on global memory.
+    float ahead[prefixes_], ahead_max = 0.0f;
+    auto fetch = [&](tile_cursor const& where) {
+        uint32_t const column_tile = where.column_tile(p);
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k) {
-            inv_q[k] = p.q_inv[static_cast<size_t>(k) * p.rows_q + row];
-            row_beta[k] = beta * inv_q[k];
-            row_gain[k] = constants.two_beta_weight * inv_q[k];
+        for (int k = 0; k < prefixes_; ++k)
+            ahead[k] = __ldg(p.c_inv + static_cast<size_t>(k) * p.rows_c + column_tile * fwd_cols + half * 32 + lane);
+        if (lane < prefixes_) ahead_max = __ldg(p.c_tile_max + static_cast<size_t>(lane) * column_tiles + column_tile);
+    };
+    auto park = [&](uint32_t into) {
+#pragma unroll
+        for (int k = 0; k < prefixes_; ++k) staged_norms[(into * 8 + k) * 32 + lane] = ahead[k];
+        if (lane < prefixes_) staged_max[into * 8 + lane] = ahead_max;
+        __syncwarp();
+    };
+    fetch(cursor);
+    park(0);
+
+    float inv_q[prefixes_], row_beta[prefixes_];
+    float loss[prefixes_], coefficient[prefixes_], g = 0.0f, ga = 0.0f;
+    uint32_t row = 0;
+    uint64_t global_row = 0;
+
+    while (cursor.valid(p)) {
+        tile_cursor const following = cursor.next(p);
+        bool const more = following.valid(p);
+        if (more) fetch(following);
+        uint32_t const strip = cursor.item / p.runs_per_strip, run = cursor.item % p.runs_per_strip;
+        if (cursor.t == 0) {
+            row = strip * fwd_rows + row_local;
+            global_row = p.query_base + row;
+#pragma unroll
+            for (int k = 0; k < prefixes_; ++k) {
+                inv_q[k] = __ldg(p.q_inv + static_cast<size_t>(k) * p.rows_q + row);
+                row_beta[k] = beta * inv_q[k];
+                loss[k] = 0.0f, coefficient[k] = 0.0f;
+            }
+            g = 0.0f, ga = 0.0f;
         }
-        float loss[prefixes_], coefficient[prefixes_], g = 0.0f, ga = 0.0f;
+        uint32_t const column_tile = cursor.column_tile(p);
+        uint32_t const column0 = column_tile * fwd_cols + half * 32;
+        float const* const norms_now = staged_norms + buffer * 8 * 32;
+        // Is this a tile where every cell is a plain negative off the cosine floor?
+        uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
+        uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
+        bool special = first_column < first_row + fwd_rows + 1 && first_row < first_column + fwd_cols + 1;
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k) loss[k] = 0.0f, coefficient[k] = 0.0f;
+        for (int k = 0; k < prefixes_; ++k) special |= inv_q[k] * staged_max[buffer * 8 + k] >= 100.0f;
+        special = __any_sync(0xFFFFFFFFu, special);
 
-        for (uint32_t t = 0; t < p.tiles_per_run; ++t, ++tile_local) {
-            uint32_t const column_tile = run * p.tiles_per_run + t;
-            uint32_t const column0 = column_tile * fwd_cols + half * 32;
-            // Is this a tile where every cell is a plain negative off the cosine floor?
-            uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
-            uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
-            bool special = first_column < first_row + fwd_rows + 1 && first_row < first_column + fwd_cols + 1;
-#pragma unroll
-            for (int k = 0; k < prefixes_; ++k)
-                special |= inv_q[k] * p.c_tile_max[static_cast<size_t>(k) * column_tiles + column_tile] >= 100.0f;
-            special = __any_sync(0xFFFFFFFFu, special);
-
-            if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u,
-                           ctx, site_fwd_tile_full, tile_local))
-                return;
-            tcgen05_fence_after();
+        if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u, ctx,
+                       site_fwd_tile_full, tile_local))
+            return;
+        tcgen05_fence_after();
 
 #pragma unroll 1
-            for (int chunk = 0; chunk < chunks_per_half; ++chunk) {
-                uint32_t const column = column0 + chunk * columns;
-                uint32_t d[prefixes_][columns];
+        for (int chunk = 0; chunk < chunks_per_half; ++chunk) {
+            uint32_t const column = column0 + chunk * columns;
+            uint32_t d[prefixes_][columns];
 #pragma unroll
-                for (int k = 0; k < prefixes_; ++k) {
-                    uint32_t const slot = (tile_local * prefixes_ + (prefixes_ - 1 - k)) % fwd_slots;
-                    tmem_load_columns<columns>(lane_base + slot * fwd_slot_columns + half * 32 + chunk * columns, d[k]);
+            for (int k = 0; k < prefixes_; ++k) {
+                uint32_t const slot = (tile_local * prefixes_ + (prefixes_ - 1 - k)) % fwd_slots;
+                tmem_load_columns<columns>(lane_base + slot * fwd_slot_columns + half * 32 + chunk * columns, d[k]);
+            }
+            tmem_load_wait();
+            float prefix[columns];
+#pragma unroll
+            for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < prefixes_; ++k) {
+                float inv_c[columns];
+                float4 const* source = reinterpret_cast<float4 const*>(norms_now + k * 32 + chunk * columns);
+#pragma unroll
+                for (int v = 0; v < columns / 4; ++v) {
+                    float4 const four = source[v];
+                    inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
                 }
-                tmem_load_wait();
-                float prefix[columns];
+                if (!special) {
 #pragma unroll
-                for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
-#pragma unroll
-                for (int k = 0; k < prefixes_; ++k) {
-                    float inv_c[columns];
-                    float4 const* source = reinterpret_cast<float4 const*>(p.c_inv + static_cast<size_t>(k) * p.rows_c + column);
-#pragma unroll
-                    for (int v = 0; v < columns / 4; ++v) {
-                        float4 const four = __ldg(source + v);
-                        inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
+                    for (int c = 0; c < columns; ++c) {
+                        prefix[c] += __uint_as_float(d[k][c]);
+                        d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], bias, loss[k], g, ga, coefficient[k]));
                     }
-                    if (!special) {
+                } else {
 #pragma unroll
-                        for (int c = 0; c < columns; ++c) {
-                            prefix[c] += __uint_as_float(d[k][c]);
-                            d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], row_gain[k], bias, loss[k], g,
-                                                                ga, coefficient[k]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < columns; ++c) {
-                            prefix[c] += __uint_as_float(d[k][c]);
-                            d[k][c] = __float_as_uint(cell_general(prefix[c], inv_q[k], inv_c[c], constants, global_row,
-                                                                   p.candidate_base + column + c, p.spec_code, loss[k], g, ga,
-                                                                   coefficient[k]));
-                        }
+                    for (int c = 0; c < columns; ++c) {
+                        prefix[c] += __uint_as_float(d[k][c]);
+                        d[k][c] = __float_as_uint(cell_general(prefix[c], inv_q[k], inv_c[c], constants, global_row,
+                                                               p.candidate_base + column + c, p.spec_code, loss[k], g, ga,
+                                                               coefficient[k]));
                     }
-                }
-                // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
-                float running[columns];
-#pragma unroll
-                for (int c = 0; c < columns; ++c) running[c] = 0.0f;
-#pragma unroll
-                for (int k = prefixes_ - 1; k >= 0; --k) {
-                    uint32_t packed[columns / 2];
-#pragma unroll
-                    for (int c = 0; c < columns; c += 2) {
-                        running[c] += __uint_as_float(d[k][c]);
-                        running[c + 1] += __uint_as_float(d[k][c + 1]);
-                        packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
-                    }
-                    uint4* destination = reinterpret_cast<uint4*>(
-                        p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
-#pragma unroll
-                    for (int v = 0; v < columns / 8; ++v)
-                        destination[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
                 }
             }
-            // This warp is done with the tile's slots.
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
+            // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
+            float running[columns];
 #pragma unroll
-                for (int k = 0; k < prefixes_; ++k)
-                    mbar_arrive(smem_u32(&tail->slot_empty[(tile_local * prefixes_ + k) % fwd_slots]));
+            for (int c = 0; c < columns; ++c) running[c] = 0.0f;
+#pragma unroll
+            for (int k = prefixes_ - 1; k >= 0; --k) {
+                uint32_t packed[columns / 2];
+#pragma unroll
+                for (int c = 0; c < columns; c += 2) {
+                    running[c] += __uint_as_float(d[k][c]);
+                    running[c + 1] += __uint_as_float(d[k][c + 1]);
+                    packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
+                }
+                uint4* destination =
+                    reinterpret_cast<uint4*>(p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
+#pragma unroll
+                for (int v = 0; v < columns / 8; ++v)
+                    destination[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
             }
         }
-        // One partial record per (run, half, row), weight applied here.
-        uint32_t const slot = run * 2 + half;
-        float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
-        record[0] = p.weight * g;
-        record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
+        // This warp is done with the tile's slots.
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k) {
-            record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * loss[k];
-            record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] = coefficient[k];
+            for (int k = 0; k < prefixes_; ++k) mbar_arrive(smem_u32(&tail->slot_empty[(tile_local * prefixes_ + k) % fwd_slots]));
         }
+        if (more) park(buffer ^ 1u);
+        if (cursor.t + 1 == p.tiles_per_run) {
+            // One partial record per (run, half, row); the 1/N weight and the mirror cell's factor two go in here.
+            uint32_t const slot = run * 2 + half;
+            float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
+            record[0] = p.weight * g;
+            record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
+#pragma unroll
+            for (int k = 0; k < prefixes_; ++k) {
+                record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * loss[k];
+                record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] = 2.0f * p.weight * coefficient[k];
+            }
+        }
+        cursor = following;
+        buffer ^= 1u;
+        ++tile_local;
     }
 }
 
@@ -396,7 +446,8 @@ __global__ void __launch_bounds__(fwd_threads, 1)
     wait_context const ctx{p.status, p.budget_ns, &tail->abort_flag};
 
     if (warp < fwd_epilogue_warps) {
-        epilogue_role<prefixes_>(p, tail, tmem_base, ctx, warp, lane);
+        epilogue_role<prefixes_>(p, tail, reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + fwd_tail_bytes), tmem_base,
+                                 ctx, warp, lane);
     } else if (warp == fwd_producer_warp) {
         if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx);
     } else if (warp == fwd_mma_warp) {

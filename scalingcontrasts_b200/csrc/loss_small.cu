@@ -126,13 +126,13 @@ __global__ void __launch_bounds__(256)
     fold_partials_kernel(float const* __restrict__ partials, float* __restrict__ accumulators, uint32_t rows, uint32_t slots,
                          uint32_t quantities) {
     uint32_t const row = blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t const quantity = blockIdx.y;
     if (row >= rows) return;
-    for (uint32_t quantity = 0; quantity < quantities; ++quantity) {
-        float total = 0;
-        for (uint32_t slot = 0; slot < slots; ++slot)
-            total += partials[(static_cast<size_t>(slot) * quantities + quantity) * rows + row];
-        accumulators[static_cast<size_t>(quantity) * rows + row] += total;
-    }
+    float total = 0;
+#pragma unroll 8
+    for (uint32_t slot = 0; slot < slots; ++slot)
+        total += partials[(static_cast<size_t>(slot) * quantities + quantity) * rows + row];
+    accumulators[static_cast<size_t>(quantity) * rows + row] += total;
 }
 
 // Row accumulators are laid out [quantity, row] with quantities: 0 bias grad, 1 log-beta grad, 2..2+K prefix losses,
@@ -293,7 +293,8 @@ void launch_pull(void const* src0, void* dst0, size_t bytes0, void const* src1, 
 
 void launch_fold_partials(float const* partials, float* row_accumulators, uint32_t rows, uint32_t slots,
                           uint32_t quantities, cudaStream_t stream) {
-    fold_partials_kernel<<<blocks_of(rows, 256), 256, 0, stream>>>(partials, row_accumulators, rows, slots, quantities);
+    fold_partials_kernel<<<dim3(blocks_of(rows, 256), quantities), 256, 0, stream>>>(partials, row_accumulators, rows, slots,
+                                                                                   quantities);
     check_launch("fold_partials");
 }
 

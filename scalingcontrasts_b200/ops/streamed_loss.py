@@ -181,7 +181,7 @@ class StreamedLoss:
         ext.transpose(candidates.data_ptr(), self.transposed_candidates.data_ptr(), self.candidate_rows, self.hidden, s)
         ext.backward(self.similarity_gradients.data_ptr(), self.transposed_candidates.data_ptr(),
                      self.query_gradient.data_ptr(), self.status.data_ptr(), self.rows, self.candidate_rows, self.hidden,
-                     list(self.ladder.ends), self.backward_split, self.budget_ns, s)
+                     list(self.ladder.ends), self.backward_split, 2.0 / float(live), self.budget_ns, s)
 
     def finish(self, queries: torch.Tensor, gradient_out: Optional[torch.Tensor] = None,
                summands: Optional[torch.Tensor] = None, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:

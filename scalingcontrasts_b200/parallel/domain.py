@@ -234,6 +234,8 @@ class DeviceDomain(Domain):
         handle = ext.NativeDomain(index, rendezvous.rank, rendezvous.world, total, want)
         own = handle.export_replica()
         multicast_ok = want
+        notes: List[str] = [] if want else (["multicast not requested"] if not want_multicast else
+                                            ["a member's device reports no multicast support"])
         descriptors: Sequence[int] = []
         multicast_descriptor = -1
 
@@ -243,8 +245,9 @@ class DeviceDomain(Domain):
                 return -1
             try:
                 return handle.create_multicast()
-            except RuntimeError:
+            except RuntimeError as error:
                 multicast_ok = False
+                notes.append(str(error))
                 return -1
 
         try:
@@ -261,8 +264,9 @@ class DeviceDomain(Domain):
                     elif multicast_descriptor < 0:
                         raise RuntimeError("multicast object creation failed")
                     handle.add_device()
-                except RuntimeError:
+                except RuntimeError as error:
                     multicast_ok = False
+                    notes.append(str(error))
                 multicast_ok = rendezvous.all_agree(rendezvous.next_tag("mc-added"), multicast_ok)
         finally:
             for descriptor in descriptors:
@@ -274,8 +278,9 @@ class DeviceDomain(Domain):
         if want and multicast_ok:
             try:
                 handle.bind_multicast()
-            except RuntimeError:
+            except RuntimeError as error:
                 multicast_ok = False
+                notes.append(str(error))
             multicast_ok = rendezvous.all_agree(rendezvous.next_tag("mc-bound"), multicast_ok)
         handle.zero_own()
         ext.preload_kernels()
@@ -284,6 +289,7 @@ class DeviceDomain(Domain):
 
         domain = MultimemDomain() if (want and multicast_ok) else PeerDomain()
         domain._native = handle
+        domain.multicast_notes = notes  # why a peer domain was formed where a multimem one was asked for
         domain._rendezvous = rendezvous
         domain.device = torch.device("cuda", index)
         domain.members, domain.member = rendezvous.world, rendezvous.rank

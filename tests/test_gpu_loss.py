@@ -38,7 +38,7 @@ def test_prefix_norms_transpose_and_keyed_generator(ext):
     assert torch.equal(out, block.T.contiguous())
 
 
-@pytest.mark.parametrize("rows,hidden,prefixes", [(128, 64, 1), (128, 256, 3), (256, 768, 5), (128, 512, 8)])
+@pytest.mark.parametrize("rows,hidden,prefixes", [(128, 64, 1), (128, 256, 3), (256, 768, 5), (128, 2048, 8)])
 def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefixes):
     """The forward kernel's per-band gradient cubes and the backward kernel's fold, each checked on its own."""
     _float32_matmul_exact()
@@ -53,7 +53,8 @@ def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefi
     reference = CpuStreamedLoss(rows, hidden, ladder, LossSpec("self"), torch.float32, "cuda", keep_cubes=True)
     reference.begin(queries)
     reference.score(queries, candidates, 0, rows, 10.0, -10.0, 2 * rows)
-    cube = loss.similarity_gradients.float()
+    # the cube is stored without the loss's factor 2 / live; the backward kernel applies it
+    cube = loss.similarity_gradients.float() * (2.0 / (2 * rows))
     for band in range(prefixes):
         assert relative_l2(cube[band], reference.last_cubes[band]) < 6e-3, f"cube of band {band}"
     # backward alone: fold the kernel's own bfloat16 cube with a float32 matmul and compare
