@@ -8,15 +8,17 @@
 // slot of tensor memory and the UMMAs of a 16-channel step accumulate into the slot of the band that contains the
 // step, so each channel is multiplied exactly once (depth H per cell, where a sweep-and-subtract scheme spends up to
 // 2H). The eight slots form a ring: while the epilogue warps drain the K slots of tile t, the issuing thread already
-// fills the widest bands of tile t+1. The epilogue reads the K segment dots of a cell, prefix-sums them into the K
-// prefix dots, runs the cell math and suffix-sums the K gradients, all in registers.
+// fills the widest bands of tile t+1. The epilogue walks the bands narrowest first, adding each band's segment dots to
+// a running prefix dot in registers, runs the cell math, parks the band's raw-dot gradients in the tensor-memory slot
+// the dots came from, and then walks the bands widest first to form the suffix sums that go to the gradient cube.
 //
-// Warp roles (384 threads): warps 0-7 epilogue (warp w owns tensor-memory lanes 32*(w%4).. and column half w/4),
-// warp 8 TMA producer, warp 9 UMMA issuer and tensor-memory owner, warps 10-11 peer pull (plain 16-byte loads from
-// the peer's replica, plain stores to local staging; never a TMA load from another GPU's memory).
+// Warp roles (608 threads): warps 0-15 epilogue (warp w owns tensor-memory lanes 32*(w%4).. and the 16 columns w/4 of
+// the tile; four warps per scheduler keep the issue slots busy), warp 16 TMA producer, warp 17 UMMA issuer and
+// tensor-memory owner, warp 18 peer pull (plain 16-byte loads from the peer's replica, plain stores to local staging;
+// never a TMA load from another GPU's memory).
 //
 // A CTA walks work items (row strip, run of consecutive candidate tiles) in a fixed round-robin order and writes one
-// partial record per (run, column half, row): the fold over runs happens later in run order, so the loss summands do
+// partial record per (run, column quarter, row): the fold over runs happens later in run order, so the loss summands do
 // not depend on scheduling.
 //
 // Parity: forward_tile_cuda_ and score_forward_row_ (scalingcontrasts.cuh:688-1040) and fold of its row partials;
@@ -39,11 +41,13 @@ constexpr uint32_t fwd_stages = 6;
 constexpr uint32_t fwd_slots = 8;
 constexpr uint32_t fwd_slot_columns = 64;
 constexpr uint32_t fwd_tmem_columns = 512;
-constexpr uint32_t fwd_epilogue_warps = 8;
-constexpr uint32_t fwd_producer_warp = 8;
-constexpr uint32_t fwd_mma_warp = 9;
-constexpr uint32_t fwd_first_pull_warp = 10;
-constexpr uint32_t fwd_pull_warps = 2;
+constexpr uint32_t fwd_epilogue_warps = 16;
+constexpr uint32_t fwd_epilogue_threads = fwd_epilogue_warps * 32;
+constexpr uint32_t fwd_chunk_columns = 16; // columns of a tile that one epilogue warp owns
+constexpr uint32_t fwd_producer_warp = 16;
+constexpr uint32_t fwd_mma_warp = 17;
+constexpr uint32_t fwd_first_pull_warp = 18;
+constexpr uint32_t fwd_pull_warps = 1;
 constexpr uint32_t fwd_threads = 32 * (fwd_epilogue_warps + 2 + fwd_pull_warps);
 constexpr uint32_t fwd_q_bytes = fwd_rows * fwd_depth * 2;
 constexpr uint32_t fwd_c_bytes = fwd_cols * fwd_depth * 2;
@@ -60,7 +64,14 @@ struct fwd_tail {
     uint32_t abort_flag;
 };
 constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
-constexpr uint32_t fwd_shared_bytes = 1024 + fwd_stages * fwd_stage_bytes + fwd_tail_bytes + 8 * 2 * (8 * 32 + 8) * 4;
+// Per epilogue warp: [2 buffers][prefixes][16 columns] candidate inverse norms, then [2][8] tile maxima.
+constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_chunk_columns + 8);
+constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
+// Per epilogue thread: inverse norm, loss and coefficient of every prefix, laid out [3 * prefixes][thread].
+constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
+constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
+    return 1024 + fwd_stages * fwd_stage_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
+}
 
 struct fwd_params {
     float const* q_inv;
@@ -106,11 +117,9 @@ __device__ __forceinline__ float cell_fast(float prefix_dot, float inv_c, float 
 }
 
 // Any cell: positives, the diagonal, floored cosines.
-__device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, float inv_c, row_constants const& k,
-                                              uint64_t global_row, uint64_t global_column, uint32_t spec_code, float& loss,
-                                              float& g, float& ga, float& coefficient) {
-    bool const own = global_row == global_column;
-    bool const partner = (spec_code & 1u) != 0u && (global_row ^ 1ull) == global_column;
+__device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, float inv_c, row_constants const& k, bool own,
+                                              bool partner, uint32_t spec_code, float& loss, float& g, float& ga,
+                                              float& coefficient) {
     uint32_t const diagonal = (spec_code >> 1) & 3u; // 0 own, 1 negative, 2 skip
     float z = partner ? 1.0f : -1.0f;
     float mask = 1.0f;
@@ -135,22 +144,14 @@ __device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, flo
     return raw;
 }
 
-template <int prefixes_>
-struct fwd_chunk {
-    static constexpr int columns = prefixes_ <= 5 ? 16 : 8;
-};
-
-__device__ __forceinline__ void tmem_load_8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
+__device__ __forceinline__ void tmem_store_16(uint32_t taddr, uint32_t const (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
-template <int columns_>
-__device__ __forceinline__ void tmem_load_columns(uint32_t taddr, uint32_t (&r)[columns_]) {
-    if constexpr (columns_ == 16) tmem_load_16(taddr, r);
-    else tmem_load_8(taddr, r);
-}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- roles ------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensorMap const* c_map, fwd_params const& p,
@@ -230,50 +231,58 @@ struct tile_cursor {
     }
 };
 
-// Per-warp staging of a tile's candidate norms: [2 buffers][prefixes][32 columns] inverse norms, then [2][8] tile maxima.
-constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * 32 + 8);
-constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
-
+// Sixteen epilogue warps: warp w owns tensor-memory lanes 32*(w%4).. (a quarter of the tile's rows) and the 16 columns
+// w/4 of the tile. The loop over prefixes is rolled (small code, few registers, four warps per scheduler): a prefix's
+// segment dots come out of tensor memory, its raw-dot gradients go back into the same slot, and a second rolled pass
+// reads them widest first to form the suffix sums. Per-thread sums that are indexed by prefix live in shared memory.
 template <int prefixes_>
-__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, float* norm_staging, uint32_t tmem_base,
-                                              wait_context const& ctx, uint32_t warp, uint32_t lane) {
-    constexpr int columns = fwd_chunk<prefixes_>::columns;
-    constexpr int chunks_per_half = 32 / columns;
-    uint32_t const quadrant = warp % 4, half = warp / 4;
+__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, float* norm_staging, float* thread_state,
+                                              uint32_t tmem_base, wait_context const& ctx, uint32_t warp, uint32_t lane) {
+    constexpr int columns = fwd_chunk_columns;
+    constexpr int norm_count = prefixes_ * columns;
+    constexpr int ahead_count = (norm_count + 31) / 32;
+    uint32_t const quadrant = warp % 4, quarter = warp / 4;
     uint32_t const row_local = quadrant * 32 + lane;
-    uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16);
+    uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16) + quarter * columns;
     uint32_t const column_tiles = p.rows_c / fwd_cols;
     uint32_t const quantities = 2 + 2 * prefixes_;
     float const beta = p.scalars != nullptr ? __ldg(p.scalars) : p.beta;
     float const bias = p.scalars != nullptr ? __ldg(p.scalars + 1) : p.bias;
     row_constants const constants{beta, bias, p.weight, beta};
-    float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][prefixes_][32]
-    float* const staged_max = staged_norms + 2 * 8 * 32;                        // [2][8]
+    float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][8][16]
+    float* const staged_max = staged_norms + 2 * 8 * columns;                   // [2][8]
+    float* const mine = thread_state + threadIdx.x;                             // [3 * prefixes_] strided by the thread count
     uint32_t tile_local = 0, buffer = 0;
 
     tile_cursor cursor{blockIdx.x, 0};
     if (!cursor.valid(p)) return;
     // Norms of a tile's candidates are fetched one tile ahead into registers and parked in this warp's shared-memory
     // buffer, so the cell loop reads them with broadcast shared loads instead of waiting on global memory.
-    float ahead[prefixes_], ahead_max = 0.0f;
+    float ahead[ahead_count], ahead_max = 0.0f;
     auto fetch = [&](tile_cursor const& where) {
         uint32_t const column_tile = where.column_tile(p);
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k)
-            ahead[k] = __ldg(p.c_inv + static_cast<size_t>(k) * p.rows_c + column_tile * fwd_cols + half * 32 + lane);
+        for (int j = 0; j < ahead_count; ++j) {
+            uint32_t const index = lane + 32 * j; // (prefix, column) = (index / 16, index % 16)
+            if (index < norm_count)
+                ahead[j] = __ldg(p.c_inv + static_cast<size_t>(index / columns) * p.rows_c + column_tile * fwd_cols +
+                                 quarter * columns + index % columns);
+        }
         if (lane < prefixes_) ahead_max = __ldg(p.c_tile_max + static_cast<size_t>(lane) * column_tiles + column_tile);
     };
     auto park = [&](uint32_t into) {
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k) staged_norms[(into * 8 + k) * 32 + lane] = ahead[k];
+        for (int j = 0; j < ahead_count; ++j) {
+            uint32_t const index = lane + 32 * j;
+            if (index < norm_count) staged_norms[into * 8 * columns + index] = ahead[j];
+        }
         if (lane < prefixes_) staged_max[into * 8 + lane] = ahead_max;
         __syncwarp();
     };
     fetch(cursor);
     park(0);
 
-    float inv_q[prefixes_], row_beta[prefixes_];
-    float loss[prefixes_], coefficient[prefixes_], g = 0.0f, ga = 0.0f;
+    float g = 0.0f, ga = 0.0f;
     uint32_t row = 0;
     uint64_t global_row = 0;
 
@@ -287,21 +296,21 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
             global_row = p.query_base + row;
 #pragma unroll
             for (int k = 0; k < prefixes_; ++k) {
-                inv_q[k] = __ldg(p.q_inv + static_cast<size_t>(k) * p.rows_q + row);
-                row_beta[k] = beta * inv_q[k];
-                loss[k] = 0.0f, coefficient[k] = 0.0f;
+                mine[k * fwd_epilogue_threads] = __ldg(p.q_inv + static_cast<size_t>(k) * p.rows_q + row);
+                mine[(prefixes_ + k) * fwd_epilogue_threads] = 0.0f;
+                mine[(2 * prefixes_ + k) * fwd_epilogue_threads] = 0.0f;
             }
             g = 0.0f, ga = 0.0f;
         }
         uint32_t const column_tile = cursor.column_tile(p);
-        uint32_t const column0 = column_tile * fwd_cols + half * 32;
-        float const* const norms_now = staged_norms + buffer * 8 * 32;
+        uint32_t const column = column_tile * fwd_cols + quarter * columns;
+        float const* const norms_now = staged_norms + buffer * 8 * columns;
         // Is this a tile where every cell is a plain negative off the cosine floor?
         uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
         uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
         bool special = first_column < first_row + fwd_rows + 1 && first_row < first_column + fwd_cols + 1;
 #pragma unroll
-        for (int k = 0; k < prefixes_; ++k) special |= inv_q[k] * staged_max[buffer * 8 + k] >= 100.0f;
+        for (int k = 0; k < prefixes_; ++k) special |= mine[k * fwd_epilogue_threads] * staged_max[buffer * 8 + k] >= 100.0f;
         special = __any_sync(0xFFFFFFFFu, special);
 
         if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u, ctx,
@@ -309,82 +318,92 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
             return;
         tcgen05_fence_after();
 
+        uint32_t const first_unit = tile_local * prefixes_;
+        float prefix[columns];
+#pragma unroll
+        for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
 #pragma unroll 1
-        for (int chunk = 0; chunk < chunks_per_half; ++chunk) {
-            uint32_t const column = column0 + chunk * columns;
-            uint32_t d[prefixes_][columns];
+        for (int k = 0; k < prefixes_; ++k) {
+            uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
+            uint32_t d[columns];
+            tmem_load_16(address, d);
+            float inv_c[columns];
+            float4 const* source = reinterpret_cast<float4 const*>(norms_now + k * columns);
 #pragma unroll
-            for (int k = 0; k < prefixes_; ++k) {
-                uint32_t const slot = (tile_local * prefixes_ + (prefixes_ - 1 - k)) % fwd_slots;
-                tmem_load_columns<columns>(lane_base + slot * fwd_slot_columns + half * 32 + chunk * columns, d[k]);
+            for (int v = 0; v < columns / 4; ++v) {
+                float4 const four = source[v];
+                inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
             }
+            float const inv_q = mine[k * fwd_epilogue_threads];
+            float const row_beta = beta * inv_q;
+            float loss = 0.0f, coefficient = 0.0f;
             tmem_load_wait();
-            float prefix[columns];
+            if (!special) {
 #pragma unroll
-            for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
-#pragma unroll
-            for (int k = 0; k < prefixes_; ++k) {
-                float inv_c[columns];
-                float4 const* source = reinterpret_cast<float4 const*>(norms_now + k * 32 + chunk * columns);
-#pragma unroll
-                for (int v = 0; v < columns / 4; ++v) {
-                    float4 const four = source[v];
-                    inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
+                for (int c = 0; c < columns; ++c) {
+                    prefix[c] += __uint_as_float(d[c]);
+                    d[c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta, bias, loss, g, ga, coefficient));
                 }
-                if (!special) {
+            } else {
+                // Which of this warp's 16 columns, if any, is the row's own copy or its pair partner.
+                int64_t const first = static_cast<int64_t>(p.candidate_base + column);
+                int64_t const own_at = static_cast<int64_t>(global_row) - first;
+                int64_t const partner_at = static_cast<int64_t>(global_row ^ 1ull) - first;
+                int const own_column = own_at >= 0 && own_at < columns ? static_cast<int>(own_at) : -1;
+                int const partner_column =
+                    (p.spec_code & 1u) != 0u && partner_at >= 0 && partner_at < columns ? static_cast<int>(partner_at) : -1;
 #pragma unroll
-                    for (int c = 0; c < columns; ++c) {
-                        prefix[c] += __uint_as_float(d[k][c]);
-                        d[k][c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta[k], bias, loss[k], g, ga, coefficient[k]));
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < columns; ++c) {
-                        prefix[c] += __uint_as_float(d[k][c]);
-                        d[k][c] = __float_as_uint(cell_general(prefix[c], inv_q[k], inv_c[c], constants, global_row,
-                                                               p.candidate_base + column + c, p.spec_code, loss[k], g, ga,
-                                                               coefficient[k]));
-                    }
+                for (int c = 0; c < columns; ++c) {
+                    prefix[c] += __uint_as_float(d[c]);
+                    d[c] = __float_as_uint(cell_general(prefix[c], inv_q, inv_c[c], constants, c == own_column,
+                                                        c == partner_column, p.spec_code, loss, g, ga, coefficient));
                 }
             }
-            // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
-            float running[columns];
+            tmem_store_16(address, d);
+            mine[(prefixes_ + k) * fwd_epilogue_threads] += loss;
+            mine[(2 * prefixes_ + k) * fwd_epilogue_threads] += coefficient;
+        }
+        tmem_store_wait();
+        // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
+        float running[columns];
 #pragma unroll
-            for (int c = 0; c < columns; ++c) running[c] = 0.0f;
+        for (int c = 0; c < columns; ++c) running[c] = 0.0f;
+#pragma unroll 1
+        for (int k = prefixes_ - 1; k >= 0; --k) {
+            uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
+            uint32_t d[columns];
+            tmem_load_16(address, d);
+            tmem_load_wait();
+            uint32_t packed[columns / 2];
 #pragma unroll
-            for (int k = prefixes_ - 1; k >= 0; --k) {
-                uint32_t packed[columns / 2];
-#pragma unroll
-                for (int c = 0; c < columns; c += 2) {
-                    running[c] += __uint_as_float(d[k][c]);
-                    running[c + 1] += __uint_as_float(d[k][c + 1]);
-                    packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
-                }
-                uint4* destination =
-                    reinterpret_cast<uint4*>(p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
-#pragma unroll
-                for (int v = 0; v < columns / 8; ++v)
-                    destination[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int c = 0; c < columns; c += 2) {
+                running[c] += __uint_as_float(d[c]);
+                running[c + 1] += __uint_as_float(d[c + 1]);
+                packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
             }
+            uint4* destination = reinterpret_cast<uint4*>(p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
+            destination[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            destination[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
         }
         // This warp is done with the tile's slots.
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) {
 #pragma unroll
-            for (int k = 0; k < prefixes_; ++k) mbar_arrive(smem_u32(&tail->slot_empty[(tile_local * prefixes_ + k) % fwd_slots]));
+            for (int k = 0; k < prefixes_; ++k) mbar_arrive(smem_u32(&tail->slot_empty[(first_unit + k) % fwd_slots]));
         }
         if (more) park(buffer ^ 1u);
         if (cursor.t + 1 == p.tiles_per_run) {
-            // One partial record per (run, half, row); the 1/N weight and the mirror cell's factor two go in here.
-            uint32_t const slot = run * 2 + half;
+            // One partial record per (run, column quarter, row); the 1/N weight and the mirror cell's factor two go in here.
+            uint32_t const slot = run * 4 + quarter;
             float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
             record[0] = p.weight * g;
             record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
 #pragma unroll
             for (int k = 0; k < prefixes_; ++k) {
-                record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * loss[k];
-                record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] = 2.0f * p.weight * coefficient[k];
+                record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * mine[(prefixes_ + k) * fwd_epilogue_threads];
+                record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] =
+                    2.0f * p.weight * mine[(2 * prefixes_ + k) * fwd_epilogue_threads];
             }
         }
         cursor = following;
@@ -402,9 +421,12 @@ __device__ __forceinline__ void pull_role(pull_request const& request, uint32_t 
         uint4 const* src = static_cast<uint4 const*>(request.src[part]);
         uint4* dst = static_cast<uint4*>(request.dst[part]);
         size_t index = thread;
-        for (; index + 3 * threads < vectors; index += 4 * threads) {
-            uint4 const a = src[index], b = src[index + threads], c = src[index + 2 * threads], d = src[index + 3 * threads];
-            dst[index] = a, dst[index + threads] = b, dst[index + 2 * threads] = c, dst[index + 3 * threads] = d;
+        for (; index + 7 * threads < vectors; index += 8 * threads) {
+            uint4 held[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) held[u] = src[index + u * threads];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) dst[index + u * threads] = held[u];
         }
         for (; index < vectors; index += threads) dst[index] = src[index];
     }
@@ -446,8 +468,8 @@ __global__ void __launch_bounds__(fwd_threads, 1)
     wait_context const ctx{p.status, p.budget_ns, &tail->abort_flag};
 
     if (warp < fwd_epilogue_warps) {
-        epilogue_role<prefixes_>(p, tail, reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + fwd_tail_bytes), tmem_base,
-                                 ctx, warp, lane);
+        float* const norm_staging = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + fwd_tail_bytes);
+        epilogue_role<prefixes_>(p, tail, norm_staging, norm_staging + fwd_norm_bytes / 4, tmem_base, ctx, warp, lane);
     } else if (warp == fwd_producer_warp) {
         if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx);
     } else if (warp == fwd_mma_warp) {
@@ -486,14 +508,15 @@ CUtensorMap make_map_2d(void const* base, uint64_t inner, uint64_t outer, uint32
 
 template <int prefixes_>
 void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, fwd_params const& p, int blocks, cudaStream_t stream) {
-    require(cudaFuncSetAttribute(forward_kernel<prefixes_>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_shared_bytes),
+    require(cudaFuncSetAttribute(forward_kernel<prefixes_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fwd_shared_bytes(prefixes_)),
             "raising the forward kernel's shared memory");
-    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes, stream>>>(q_map, c_map, p);
+    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes(prefixes_), stream>>>(q_map, c_map, p);
 }
 
 } // namespace
 
-uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run) { return 2 * (rows_c / fwd_cols) / tiles_per_run; }
+uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run) { return 4 * (rows_c / fwd_cols) / tiles_per_run; }
 uint32_t forward_quantities(uint32_t prefixes) { return 2 + 2 * prefixes; }
 
 uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors) {

@@ -112,10 +112,9 @@ class StreamedLoss:
         self.tiles_per_run = int(ext.forward_choose_tiles_per_run(rows, self.candidate_rows, self.multiprocessors))
         self.partial_slots = int(ext.forward_partial_slots(self.candidate_rows, self.tiles_per_run))
         self.quantities = int(ext.forward_quantities(k))
-        if backward_split <= 0:
-            tiles = sum(-(-ladder.width(b) // 192) for b in range(k)) * (rows // 128)
-            backward_split = max(1, min(8, (2 * self.multiprocessors) // max(tiles, 1)))
-        self.backward_split = int(backward_split)
+        # One CTA per output tile keeps the gradient fold a plain read-modify-write, hence bit-reproducible; a larger
+        # split divides the candidate range between CTAs that add with atomics (faster for tiny blocks, order-dependent).
+        self.backward_split = max(1, int(backward_split))
         f32 = dict(dtype=torch.float32, device=self.device)
         bf16 = dict(dtype=torch.bfloat16, device=self.device)
         self.query_norms = BlockNorms(k, rows, device=self.device)
