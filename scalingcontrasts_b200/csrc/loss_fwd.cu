@@ -62,6 +62,7 @@ struct fwd_tail {
     uint64_t tile_full[fwd_tile_barriers];
     uint32_t tmem_base;
     uint32_t abort_flag;
+    uint32_t band_starts[64]; // per 64-channel chunk, where bands begin (see mma_role); hidden <= 4096
 };
 constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
 // Per epilogue warp: [2 buffers][prefixes][16 columns] candidate inverse norms, then [2][8] tile maxima.
@@ -176,42 +177,57 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
     }
 }
 
+// The UMMA issuer is one thread, and a 128 x 64 x 16 UMMA occupies the tensor pipe for only ~32 cycles, so the loop
+// around each issue has to be a handful of instructions: descriptors are a constant high word plus a low word that
+// advances by fixed amounts, and where a band begins (walking the channels downwards) is read from a per-chunk flag
+// word prepared once in shared memory instead of being searched in the ladder.
 template <int prefixes_>
 __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_base, fwd_tail* tail, uint32_t tmem_base,
                                          wait_context const& ctx) {
     constexpr uint32_t idesc = umma_idesc_bf16(fwd_rows, fwd_cols);
+    constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
+    uint32_t const chunks = p.hidden / fwd_depth;
+    // band_starts[chunk] holds one byte per 16-channel step of the chunk: non-zero when, walking downwards, the step is
+    // the first of a band (the topmost step, or the step just below a band's first channel).
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        uint32_t word = 0;
+        for (uint32_t sub = 0; sub < 4; ++sub) {
+            uint32_t const above = (chunk * 4 + sub + 1) * 16; // first channel above this step
+            bool starts = above == p.hidden;
+            for (uint32_t band = 0; band + 1 < p.ladder.count; ++band) starts |= p.ladder.ends[band] == above;
+            word |= (starts ? 1u : 0u) << (8 * sub);
+        }
+        tail->band_starts[chunk] = word;
+    }
+    uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
     uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0;
-    int const steps = static_cast<int>(p.hidden / 16);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
-            int band = prefixes_; // none yet
             uint32_t slot_address = 0, accumulate = 0;
-            for (int step = steps - 1; step >= 0; --step) {
-                uint32_t const sub = static_cast<uint32_t>(step) & 3u;
-                if (sub == 3u) {
-                    if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
-                    tcgen05_fence_after();
+            for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
+                uint32_t const starts = tail->band_starts[chunk];
+                if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
+                tcgen05_fence_after();
+                uint32_t const low = low_base + stage * (fwd_stage_bytes >> 4);
+#pragma unroll
+                for (int sub = 3; sub >= 0; --sub) {
+                    if ((starts >> (8 * sub)) & 0xFFu) {
+                        uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
+                        if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
+                        tcgen05_fence_after();
+                        slot_address = tmem_base + slot * fwd_slot_columns;
+                        accumulate = 0;
+                        ++unit;
+                    }
+                    uint32_t const q_low = low + static_cast<uint32_t>(sub) * 2u; // 32 bytes per 16-channel step
+                    uint64_t q_descriptor, c_descriptor;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(q_descriptor) : "r"(q_low), "r"(descriptor_high));
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(c_descriptor) : "r"(q_low + (fwd_q_bytes >> 4)), "r"(descriptor_high));
+                    umma_bf16(slot_address, q_descriptor, c_descriptor, idesc, accumulate);
+                    accumulate = 1;
                 }
-                uint32_t const channel = static_cast<uint32_t>(step) * 16u;
-                int next_band = band == prefixes_ ? prefixes_ - 1 : band;
-                while (next_band > 0 && channel < p.ladder.ends[next_band - 1]) --next_band;
-                if (next_band != band) {
-                    band = next_band;
-                    uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
-                    if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
-                    tcgen05_fence_after();
-                    slot_address = tmem_base + slot * fwd_slot_columns;
-                    accumulate = 0;
-                    ++unit;
-                }
-                uint32_t const q_address = stages_base + stage * fwd_stage_bytes + sub * 32u;
-                umma_bf16(slot_address, umma_desc_k_major_sw128(q_address, 1024u),
-                          umma_desc_k_major_sw128(q_address + fwd_q_bytes, 1024u), idesc, accumulate);
-                accumulate = 1;
-                if (sub == 0u) {
-                    umma_commit(smem_u32(&tail->stage_empty[stage]));
-                    if (++stage == fwd_stages) stage = 0, phase ^= 1u;
-                }
+                umma_commit(smem_u32(&tail->stage_empty[stage]));
+                if (++stage == fwd_stages) stage = 0, phase ^= 1u;
             }
             umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
             ++tile_local;
@@ -528,8 +544,8 @@ uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int mult
 }
 
 void launch_forward(forward_arguments const& a, cudaStream_t stream) {
-    if (a.rows_q % fwd_rows || a.rows_c % fwd_cols || a.hidden % fwd_depth)
-        throw std::runtime_error("forward: rows must be multiples of 128 (queries) and 64 (candidates), hidden of 64");
+    if (a.rows_q % fwd_rows || a.rows_c % fwd_cols || a.hidden % fwd_depth || a.hidden > 4096)
+        throw std::runtime_error("forward: rows must be multiples of 128 (queries) and 64 (candidates), hidden of 64 up to 4096");
     if (a.ladder.count < 1 || a.ladder.count > 8 || a.ladder.ends[a.ladder.count - 1] != a.hidden)
         throw std::runtime_error("forward: the ladder's widest prefix must equal hidden");
     for (uint32_t band = 0; band < a.ladder.count; ++band)
