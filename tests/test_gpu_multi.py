@@ -1,0 +1,69 @@
+"""Multi-GPU checks, one process per GPU, driven through the command line modes (which is also how a user runs them).
+They need at least two visible GPUs and are skipped otherwise."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpus() -> int:
+    return min(torch.cuda.device_count(), 8) if torch.cuda.is_available() else 0
+
+
+def _run(*arguments: str, timeout: int = 600) -> list:
+    environment = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    result = subprocess.run([sys.executable, "-m", "scalingcontrasts_b200.cli", *arguments], cwd=ROOT, env=environment,
+                            capture_output=True, text=True, timeout=timeout)
+    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    return [line.split(",") for line in result.stdout.strip().splitlines() if "," in line]
+
+
+needs_two = pytest.mark.skipif(_gpus() < 2, reason="needs at least two GPUs")
+
+
+@needs_two
+@pytest.mark.parametrize("flags", [(), ("--no-multicast",)], ids=["multimem", "peer"])
+def test_collectives_are_exact_and_repeat_bit_for_bit(flags):
+    rows = _run("collectives", "--gpus", str(_gpus()), "--min-kib", "1", "--max-mib", "4", "--repeats", "5", "--windows", "2", *flags)
+    validation = [row for row in rows if row[0] == "validation"][0]
+    assert int(validation[1]) == _gpus()
+    assert (int(validation[3]), int(validation[4]), int(validation[6])) == (0, 0, 0)
+    assert any(row[0] == "barrier" for row in rows) and any(row[0] == "all_reduce" for row in rows)
+    assert all(float(row[3]) > 0 for row in rows if row[0] in ("all_reduce", "reduce_scatter"))
+
+
+@needs_two
+@pytest.mark.parametrize("positives", ["self", "pairs"])
+def test_box_oracle_against_float64(positives):
+    row = _run("oracle", "--gpus", str(_gpus()), "--rows", "128", "--hidden", "768", "--prefixes", "5", "--inputs", "normal",
+               "--seed", "1", "--positives", positives)[-1]
+    exact, measured, error, disagreeing = float(row[5]), float(row[6]), float(row[7]), int(row[8])
+    assert int(row[4]) == _gpus()
+    assert abs(measured - exact) <= 2e-6 * abs(exact)
+    assert error < 4e-3
+    assert disagreeing == 0  # every rank holds the same loss, bit for bit
+
+
+@needs_two
+def test_box_and_train_modes_run():
+    box = _run("box", "--gpus", str(_gpus()), "--rows", "512", "--hidden", "256", "--prefixes", "3", "--windows", "2")[-1]
+    assert box[0] == "box" and int(box[4]) == _gpus() and float(box[6]) > 0
+    train = _run("train", "--gpus", str(_gpus()), "--rows", "512", "--hidden", "256", "--prefixes", "3", "--warm", "3", "--steps", "10")[-1]
+    assert train[0] == "train" and float(train[5]) > 0
+
+
+@needs_two
+def test_gradient_reducer_matches_nccl_sum():
+    script = os.path.join(ROOT, "tests", "multi_reducer_check.py")
+    environment = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={min(_gpus(), 4)}",
+                             "--master-addr", "127.0.0.1", "--master-port", "29631", script], cwd=ROOT, env=environment,
+                            capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    assert "reducer ok" in result.stdout
