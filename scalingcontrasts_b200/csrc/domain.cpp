@@ -111,7 +111,7 @@ void native_domain::add_device() {
 void native_domain::map_replicas() {
     for (int m = 0; m < members_; ++m)
         if (!have_handle_[m]) throw std::runtime_error("domain: a peer's replica was never imported");
-    SC_DRIVER(cuMemAddressReserve, &replicas_base_, stride_ * members_, stride_, 0, 0);
+    SC_DRIVER(cuMemAddressReserve, &replicas_base_, stride_ * members_, 0, 0, 0);
     CUmemAccessDesc access{};
     access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     access.location.id = device_;
@@ -127,7 +127,7 @@ void native_domain::bind_multicast() {
     if (!have_multicast_handle_) throw std::runtime_error("domain: no multicast object to bind");
     SC_DRIVER(cuMulticastBindMem, multicast_handle_, 0, handles_[member_], 0, stride_, 0);
     bound_ = true;
-    SC_DRIVER(cuMemAddressReserve, &multicast_base_, stride_, stride_, 0, 0);
+    SC_DRIVER(cuMemAddressReserve, &multicast_base_, stride_, 0, 0, 0);
     SC_DRIVER(cuMemMap, multicast_base_, stride_, 0, multicast_handle_, 0);
     multicast_mapped_ = true;
     CUmemAccessDesc access{};

@@ -39,7 +39,7 @@ class GradientReducer:
         self.domain, self.scale = domain, float(scale)
         self.enabled = domain is not None and getattr(domain, "members", 1) > 1 and hasattr(domain, "alloc")
         self.buckets: List[_Bucket] = []
-        self._by_parameter = {}
+        self._by_parameter = {}  # id(parameter) -> (bucket, view)
         self._handles = []
         if not self.enabled:
             return
@@ -65,9 +65,10 @@ class GradientReducer:
             cursor = bucket.offset
             per_vector = 16 // element
             for parameter in bucket.parameters:
-                bucket.views.append(domain.tensor(cursor, tuple(parameter.shape), parameter.dtype))
+                view = domain.tensor(cursor, tuple(parameter.shape), parameter.dtype)
+                bucket.views.append(view)
                 cursor += -(-parameter.numel() // per_vector) * per_vector * element
-                self._by_parameter[parameter] = bucket
+                self._by_parameter[id(parameter)] = (bucket, view)
                 self._handles.append(parameter.register_post_accumulate_grad_hook(self._on_gradient))
             domain.tensor(bucket.offset, (bucket.scalars,), bucket.dtype).zero_()
             bucket.pending = len(bucket.parameters)
@@ -82,8 +83,7 @@ class GradientReducer:
         return total + 4096
 
     def _on_gradient(self, parameter: torch.nn.Parameter) -> None:
-        bucket = self._by_parameter[parameter]
-        view = bucket.views[bucket.parameters.index(parameter)]
+        bucket, view = self._by_parameter[id(parameter)]
         if parameter.grad.data_ptr() != view.data_ptr():
             view.copy_(parameter.grad)
             parameter.grad = view
