@@ -54,7 +54,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--prefixes", type=int, default=defaults.prefixes)
     parser.add_argument("--ends", type=str, default="", help="explicit ascending prefix ends, comma separated")
     parser.add_argument("--gpus", type=int, default=0, help="GPUs to use (simulate: size of the simulated world)")
-    parser.add_argument("--windows", type=int, default=defaults.windows)
+    parser.add_argument("--windows", type=int, default=defaults.windows, help="timed windows (hosts mode: 0 prints an oracle row)")
     parser.add_argument("--max-mib", type=int, default=defaults.max_mib)
     parser.add_argument("--min-kib", type=int, default=defaults.min_kib)
     parser.add_argument("--repeats", type=int, default=defaults.repeats)

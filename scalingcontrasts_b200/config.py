@@ -98,7 +98,9 @@ class Settings:
         return replace(self, **changes)
 
     def validate(self) -> None:
-        for name in ("rows", "hidden", "prefixes", "windows", "max_mib", "repeats", "hosts"):
+        if self.windows < 0 or (self.windows == 0 and self.mode != "hosts"):
+            raise ValueError("--windows must be positive")
+        for name in ("rows", "hidden", "prefixes", "max_mib", "repeats", "hosts"):
             if getattr(self, name) <= 0:
                 raise ValueError(f"--{name.replace('_', '-')} must be positive")
         if self.host < 0 or self.host >= self.hosts:

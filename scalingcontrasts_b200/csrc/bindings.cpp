@@ -249,14 +249,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("post_embeddings", &sc::loopback_rail::post_embeddings)
         .def("post_summands",
              [](sc::loopback_rail& rail, int row, std::vector<float> const& values) {
-                 if (values.size() != 4) throw std::runtime_error("rail: a summands row holds four floats");
-                 rail.post_summands(row, values.data());
+                 rail.post_summands(row, values.data(), static_cast<int>(values.size()));
              })
         .def("await_landed", &sc::loopback_rail::await_landed, py::call_guard<py::gil_scoped_release>())
         .def("read_summands",
-             [](sc::loopback_rail const& rail, int row) {
-                 std::vector<float> out(4);
-                 rail.read_summands(row, out.data());
+             [](sc::loopback_rail const& rail, int row, int count) {
+                 std::vector<float> out(static_cast<size_t>(count));
+                 rail.read_summands(row, out.data(), count);
                  return out;
              })
         .def("inject_completion_error", &sc::loopback_rail::inject_completion_error)

@@ -2,7 +2,7 @@
 //
 // A rail connects one GPU of this host with the same-numbered GPU of another host. It keeps the reference's verbs
 // semantics: the embeddings block is written into the peer's landing buffer of the given parity and the peer sees a
-// completion carrying the byte count as immediate data; a 16-byte row of loss summands is written into the peer's
+// completion carrying the byte count as immediate data; a row of loss summands is written into the peer's
 // host-side table the same way; `await_landed` consumes one completion.
 //
 // This box has one host and no RDMA NIC, so the transport here is a loopback: the "write" is a device-to-device copy
@@ -186,14 +186,15 @@ void loopback_rail::post_embeddings(int parity, uint64_t after_stream) {
     ++posted_;
 }
 
-void loopback_rail::post_summands(int row, float const* values) {
+void loopback_rail::post_summands(int row, float const* values, int count) {
     if (!connected_) throw std::runtime_error("rail: post before connect");
     if (row < 0 || row >= hosts_) throw std::runtime_error("rail: bad summands row");
-    for (int i = 0; i < 4; ++i) remote_mailbox_->summands[row][i] = values[i];
+    if (count < 1 || count > rail_summand_floats) throw std::runtime_error("rail: a summands row holds 1..16 floats");
+    for (int i = 0; i < count; ++i) remote_mailbox_->summands[row][i] = values[i];
     std::atomic_thread_fence(std::memory_order_release);
     uint32_t const status = injected_status_;
     injected_status_ = 0;
-    push_completion(remote_mailbox_, 16u, status);
+    push_completion(remote_mailbox_, static_cast<uint32_t>(count * 4), status);
     ++posted_;
 }
 
@@ -210,10 +211,11 @@ uint32_t loopback_rail::await_landed(double timeout_seconds) {
     return immediate;
 }
 
-void loopback_rail::read_summands(int row, float* out) const {
+void loopback_rail::read_summands(int row, float* out, int count) const {
     if (row < 0 || row >= hosts_) throw std::runtime_error("rail: bad summands row");
+    if (count < 1 || count > rail_summand_floats) throw std::runtime_error("rail: a summands row holds 1..16 floats");
     std::atomic_thread_fence(std::memory_order_acquire);
-    for (int i = 0; i < 4; ++i) out[i] = own_mailbox_->summands[row][i];
+    for (int i = 0; i < count; ++i) out[i] = own_mailbox_->summands[row][i];
 }
 
 void loopback_rail::inject_completion_error(uint32_t status) { injected_status_ = status; }

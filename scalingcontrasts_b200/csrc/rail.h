@@ -12,6 +12,7 @@ namespace sc {
 
 constexpr int rail_queue_depth = 64;
 constexpr int rail_max_hosts = 64;
+constexpr int rail_summand_floats = 16; // one row of loss summands
 
 // What one side publishes so that the other can write to it. Plain bytes: it crosses processes through a file.
 struct rail_endpoint {
@@ -37,7 +38,7 @@ struct rail_completion {
 struct rail_mailbox {
     std::atomic<uint64_t> head;
     rail_completion entries[rail_queue_depth];
-    float summands[rail_max_hosts][4];
+    float summands[rail_max_hosts][rail_summand_floats];
 };
 
 class loopback_rail {
@@ -52,11 +53,11 @@ class loopback_rail {
     void connect(rail_endpoint const& remote);
     // Writes this side's embeddings into the peer's landing[parity] once `after_stream` has produced them.
     void post_embeddings(int parity, uint64_t after_stream);
-    // Writes four floats into row `row` of the peer's summands table.
-    void post_summands(int row, float const* values);
+    // Writes `count` floats (at most rail_summand_floats) into row `row` of the peer's summands table.
+    void post_summands(int row, float const* values, int count);
     // Consumes one completion; returns its immediate data. Throws on a timeout or on an error completion.
     uint32_t await_landed(double timeout_seconds);
-    void read_summands(int row, float* out) const;
+    void read_summands(int row, float* out, int count) const;
     // The next completion this side produces carries `status` instead of success (host-side fault injection).
     void inject_completion_error(uint32_t status);
     void drain();

@@ -19,13 +19,31 @@ replaces the reference's serial ``cudaMemcpyAsync`` (scalingcontrasts.cuh:1262-1
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
 from ..config import LossSpec, REFERENCE_SPEC, SUMMAND_SLOTS
 from ..ladder import Matryoshka
 from ..ops.streamed_loss import BlockNorms, PullRequest, StreamedLoss, compute_block_norms
+
+
+@dataclass
+class SourceBlock:
+    """Where one candidate block lives: in this GPU's memory (``embeddings`` / ``norms`` given), or in a domain member's
+    replica at the two offsets, from where it is pulled into local staging before it is scored."""
+
+    candidate_base: int
+    embeddings: Optional[torch.Tensor] = None
+    norms: Optional[BlockNorms] = None
+    member: int = -1
+    embeddings_offset: int = 0
+    norms_offset: int = 0
+
+    @property
+    def local(self) -> bool:
+        return self.embeddings is not None
 
 
 class BoxLoss:
@@ -67,10 +85,31 @@ class BoxLoss:
         own = sum(t.numel() * t.element_size() for t in self.staged) + sum(n.nbytes for n in self.staged_norms)
         return self.loss.bytes() + own + self.gradient.numel() * 2
 
-    def _pull_from(self, member: int, slot: int) -> PullRequest:
-        return PullRequest(self.domain.address(self._embeddings_offset, member), self.staged[slot].data_ptr(),
-                           self.rows * self.hidden * 2, self.domain.address(self._norms_offset, member),
+    def _pull(self, block: SourceBlock, slot: int) -> PullRequest:
+        return PullRequest(self.domain.address(block.embeddings_offset, block.member), self.staged[slot].data_ptr(),
+                           self.rows * self.hidden * 2, self.domain.address(block.norms_offset, block.member),
                            self.staged_norms[slot].storage.data_ptr(), self.staged_norms[slot].nbytes)
+
+    def score_sequence(self, blocks: Sequence[SourceBlock], query_base: int, live: int, beta: float, bias: float,
+                       scalars: Optional[torch.Tensor] = None, stream=None) -> None:
+        """Scores ``blocks`` in order. A block in a peer's replica is pulled into one of two staging buffers by the forward
+        launch of the block before it, so only a remote block in first position costs a launch of its own."""
+        from .._ext import native
+
+        for index, block in enumerate(blocks):
+            if block.local:
+                candidates, norms = block.embeddings, block.norms
+            else:
+                slot = (index - 1) % 2
+                if index == 0:
+                    request = self._pull(block, slot)
+                    native().pull(request.src0, request.dst0, request.bytes0, request.src1, request.dst1, request.bytes1,
+                                  self.loss.multiprocessors, (torch.cuda.current_stream() if stream is None else stream).cuda_stream)
+                candidates, norms = self.staged[slot], self.staged_norms[slot]
+            following = blocks[index + 1] if index + 1 < len(blocks) else None
+            pull = self._pull(following, index % 2) if following is not None and not following.local else None
+            self.loss.score(self.embeddings, candidates, query_base, block.candidate_base, beta, bias, live, stream,
+                            candidate_norms=norms, scalars=scalars, pull_next=pull)
 
     # ------------------------------------------------------------------------------------------------------
     def step(self, queries: torch.Tensor, beta: float = 10.0, bias: float = -10.0, scalars: Optional[torch.Tensor] = None,
@@ -82,16 +121,12 @@ class BoxLoss:
         if self.domain is not None:
             self.domain.barrier(stream)
         self.loss.begin(self.embeddings, stream, query_norms=self.norms)
-        live = members * rows
-        for p in range(members):
+        blocks: List[SourceBlock] = [SourceBlock(member * rows, self.embeddings, self.norms)]
+        for p in range(1, members):
             peer = (member + p) % members
-            if p == 0:
-                candidates, norms = self.embeddings, self.norms
-            else:
-                candidates, norms = self.staged[(p - 1) % 2], self.staged_norms[(p - 1) % 2]
-            pull = self._pull_from((member + p + 1) % members, p % 2) if p + 1 < members else None
-            self.loss.score(self.embeddings, candidates, member * rows, peer * rows, beta, bias, live, stream,
-                            candidate_norms=norms, scalars=scalars, pull_next=pull)
+            blocks.append(SourceBlock(peer * rows, member=peer, embeddings_offset=self._embeddings_offset,
+                                      norms_offset=self._norms_offset))
+        self.score_sequence(blocks, member * rows, members * rows, beta, bias, scalars, stream)
         gradient = self.gradient if gradient_out is None else gradient_out
         self.loss.finish(self.embeddings, gradient, self.summands, stream)
         if reduce and self.domain is not None:

@@ -67,3 +67,16 @@ def test_gradient_reducer_matches_nccl_sum():
                             capture_output=True, text=True, timeout=600)
     assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
     assert "reducer ok" in result.stdout
+
+
+@needs_two
+def test_hosts_mode_over_loopback_rails_against_float64():
+    """Two logical hosts on this box, their blocks crossing the rails, checked like the box oracle."""
+    gpus = _gpus() - _gpus() % 2
+    row = _run("hosts", "--hosts", "2", "--gpus", str(gpus), "--rows", "128", "--hidden", "256", "--prefixes", "3", "--inputs",
+               "normal", "--seed", "2", "--windows", "0")[-1]
+    exact, measured, error, disagreeing = float(row[5]), float(row[6]), float(row[7]), int(row[8])
+    assert row[0] == "oracle" and int(row[4]) == gpus
+    assert abs(measured - exact) <= 2e-6 * abs(exact) and error < 4e-3 and disagreeing == 0
+    timed = _run("hosts", "--hosts", "2", "--gpus", str(gpus), "--rows", "256", "--hidden", "256", "--prefixes", "3", "--windows", "2")[-1]
+    assert timed[0] == "hosts" and float(timed[6]) > 0
