@@ -107,12 +107,17 @@ struct forward_arguments {
     uint32_t spec_code;
     uint64_t budget_ns;
     pull_request pull;               // optional: bytes == 0 means nothing to pull
+    // Optional phase timers (device array of forward_trace_slots counters, zeroed by the caller): CTA 0 adds the cycles
+    // it spends in 0 producer issue, 1 producer waiting for a free stage, 2 UMMA issue, 3 UMMA waiting for a stage,
+    // 4 UMMA waiting for a slot, 5 epilogue between tiles, 6 epilogue waiting for a tile, 7 cell pass, 8 suffix pass.
+    unsigned long long* trace;
     int multiprocessors;
 };
 // Returns the number of partial slots the launch fills: 4 * rows_c / 64 / tiles_per_run.
 uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run);
 uint32_t forward_quantities(uint32_t prefixes);
 uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors);
+constexpr int forward_trace_slots = 16;
 void launch_forward(forward_arguments const& arguments, cudaStream_t stream);
 
 struct backward_arguments {

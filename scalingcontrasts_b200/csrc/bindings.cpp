@@ -184,7 +184,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              std::vector<uint32_t> const& ends, uint32_t tiles_per_run, float beta, float bias, float weight, uint64_t scalars,
              uint64_t query_base,
              uint64_t candidate_base, uint32_t spec_code, uint64_t budget_ns, uint64_t pull_src0, uint64_t pull_dst0,
-             uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1, int sms, uint64_t stream) {
+             uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1, int sms, uint64_t stream,
+             uint64_t trace) {
               sc::forward_arguments a{};
               a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
               a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
@@ -198,8 +199,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               a.pull.src[0] = pointer<void>(pull_src0), a.pull.dst[0] = pointer<void>(pull_dst0), a.pull.bytes[0] = pull_bytes0;
               a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;
               a.multiprocessors = sms;
+              a.trace = pointer<unsigned long long>(trace);
               sc::launch_forward(a, stream_of(stream));
-          });
+          },
+          py::arg("queries"), py::arg("candidates"), py::arg("q_inv"), py::arg("c_inv"), py::arg("c_tile_max"), py::arg("cube"),
+          py::arg("partials"), py::arg("status"), py::arg("rows_q"), py::arg("rows_c"), py::arg("hidden"), py::arg("ends"),
+          py::arg("tiles_per_run"), py::arg("beta"), py::arg("bias"), py::arg("weight"), py::arg("scalars"), py::arg("query_base"),
+          py::arg("candidate_base"), py::arg("spec_code"), py::arg("budget_ns"), py::arg("pull_src0"), py::arg("pull_dst0"),
+          py::arg("pull_bytes0"), py::arg("pull_src1"), py::arg("pull_dst1"), py::arg("pull_bytes1"), py::arg("sms"),
+          py::arg("stream"), py::arg("trace") = 0);
     m.def("backward", [](uint64_t cube, uint64_t transposed, uint64_t query_gradient, uint64_t status, uint32_t rows_q,
                          uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, float scale,
                          uint64_t budget_ns, uint64_t stream) {

@@ -260,6 +260,42 @@ __device__ __forceinline__ float log1p_ratio(float x) {
     return fmaf(p, x, SC_LOG1P_C0);
 }
 
+// Packed pairs of float32 in one 64-bit register: sm_100 executes add / mul / fma on both halves in one instruction,
+// which halves the issue slots of the epilogue's arithmetic.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// log1p(x) / x for both halves of a pair (the same polynomial as log1p_ratio).
+__device__ __forceinline__ uint64_t log1p_ratio2(uint64_t x) {
+    uint64_t p = pack2(SC_LOG1P_C8, SC_LOG1P_C8);
+    p = fma2(p, x, pack2(SC_LOG1P_C7, SC_LOG1P_C7));
+    p = fma2(p, x, pack2(SC_LOG1P_C6, SC_LOG1P_C6));
+    p = fma2(p, x, pack2(SC_LOG1P_C5, SC_LOG1P_C5));
+    p = fma2(p, x, pack2(SC_LOG1P_C4, SC_LOG1P_C4));
+    p = fma2(p, x, pack2(SC_LOG1P_C3, SC_LOG1P_C3));
+    p = fma2(p, x, pack2(SC_LOG1P_C2, SC_LOG1P_C2));
+    p = fma2(p, x, pack2(SC_LOG1P_C1, SC_LOG1P_C1));
+    return fma2(p, x, pack2(SC_LOG1P_C0, SC_LOG1P_C0));
+}
+
 // Matryoshka ladder by value, the form kernels take (ascending ends, zero padded).
 struct ladder_t {
     uint32_t count;

@@ -37,7 +37,9 @@ namespace {
 constexpr uint32_t fwd_rows = 128;
 constexpr uint32_t fwd_cols = 64;
 constexpr uint32_t fwd_depth = 64;
-constexpr uint32_t fwd_stages = 6;
+constexpr uint32_t fwd_max_stages = 6;
+// Ladders of up to five prefixes leave room for six stages; longer ones keep more per-thread state and get five.
+constexpr uint32_t fwd_stages_for(uint32_t prefixes) { return prefixes <= 5 ? 6u : 5u; }
 constexpr uint32_t fwd_slots = 8;
 constexpr uint32_t fwd_slot_columns = 64;
 constexpr uint32_t fwd_tmem_columns = 512;
@@ -56,8 +58,8 @@ constexpr uint32_t fwd_tile_barriers = 8;
 constexpr float log2_e = 1.4426950408889634f;
 
 struct fwd_tail {
-    uint64_t stage_full[fwd_stages];
-    uint64_t stage_empty[fwd_stages];
+    uint64_t stage_full[fwd_max_stages];
+    uint64_t stage_empty[fwd_max_stages];
     uint64_t slot_empty[fwd_slots];
     uint64_t tile_full[fwd_tile_barriers];
     uint32_t tmem_base;
@@ -70,8 +72,12 @@ constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_chunk_columns + 8);
 constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
 // Per epilogue thread: inverse norm, loss and coefficient of every prefix, laid out [3 * prefixes][thread].
 constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
+// Per epilogue warp two staging buffers of [32 rows][16 columns] bfloat16, from which the warp's patch of a band's
+// gradient cube leaves through a TMA store while the next band is being computed.
+constexpr uint32_t fwd_store_patch_bytes = 32 * fwd_chunk_columns * 2;
+constexpr uint32_t fwd_store_bytes = fwd_epilogue_warps * 2 * fwd_store_patch_bytes;
 constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
-    return 1024 + fwd_stages * fwd_stage_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
+    return 1024 + fwd_stages_for(prefixes) * fwd_stage_bytes + fwd_store_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
 }
 
 struct fwd_params {
@@ -90,7 +96,17 @@ struct fwd_params {
     uint32_t spec_code;
     uint64_t budget_ns;
     pull_request pull;
+    unsigned long long* trace; // optional: phase cycle counters of CTA 0 (see forward_trace_slots in api.h)
 };
+
+// Adds the cycles since `since` to a phase counter when tracing is on (CTA 0 only), and restarts the clock.
+__device__ __forceinline__ void trace_phase(fwd_params const& p, int slot, long long& since) {
+    if (p.trace != nullptr && blockIdx.x == 0) {
+        long long const now = clock64();
+        p.trace[slot] += static_cast<unsigned long long>(now - since);
+        since = now;
+    }
+}
 
 // ---- the cell math ----------------------------------------------------------------------------------------------
 // Accumulators are kept without the 1/N weight: `g` sums -mask*z*(1-sigmoid(s)), `ga` sums that times (logit+bias),
@@ -99,21 +115,28 @@ struct row_constants {
     float beta, bias, weight, raw_scale;
 };
 
-// A negative cell whose cosine is off the floor: z = -1, s = -(logit + bias). Returns the gradient with respect to the
-// raw dot product WITHOUT the factor 2/N (mirror cell and weight), which the backward kernel applies once per element.
-__device__ __forceinline__ float cell_fast(float prefix_dot, float inv_c, float row_beta, float bias, float& loss, float& g,
-                                           float& ga, float& coefficient) {
-    float const scale = inv_c * row_beta;                 // beta / (|q| |c|)
-    float const a = fmaf(prefix_dot, scale, bias);        // logit + bias
-    float const e = fast_ex2(-fabsf(a) * log2_e);         // exp(-|a|)
-    float const r = fast_rcp(1.0f + e);
-    float const complement = (a >= 0.0f ? 1.0f : e) * r;  // 1 - sigmoid(s) = sigmoid(a)
-    loss += fmaxf(a, 0.0f);
-    loss = fmaf(log1p_ratio(e), e, loss);
-    g += complement;
-    ga = fmaf(complement, a, ga);
-    float const raw = complement * scale;
-    coefficient = fmaf(raw, prefix_dot, coefficient);
+// A negative cell whose cosine is off the floor has z = -1 and s = -(logit + bias). The fast path handles two such cells
+// at once on packed pairs and returns their gradients with respect to the raw dot product WITHOUT the factor 2/N (mirror
+// cell and weight), which the backward kernel applies once per element. `loss`, `g`, `ga` and `coefficient` are pairs of
+// partial sums whose halves are added when the band is done.
+__device__ __forceinline__ uint64_t cell_fast2(uint64_t prefix_dot, uint64_t inv_c, uint64_t row_beta, uint64_t bias,
+                                               uint64_t& loss, uint64_t& g, uint64_t& ga, uint64_t& coefficient) {
+    uint64_t const scale = mul2(inv_c, row_beta);
+    uint64_t const a = fma2(prefix_dot, scale, bias);
+    float a0, a1;
+    unpack2(a, a0, a1);
+    float const e0 = fast_ex2(-fabsf(a0) * log2_e), e1 = fast_ex2(-fabsf(a1) * log2_e);
+    uint64_t const e = pack2(e0, e1);
+    float s0, s1;
+    unpack2(add2(e, pack2(1.0f, 1.0f)), s0, s1);
+    uint64_t const r = pack2(fast_rcp(s0), fast_rcp(s1));
+    uint64_t const complement = mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), r);
+    loss = add2(loss, pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
+    loss = fma2(log1p_ratio2(e), e, loss);
+    g = add2(g, complement);
+    ga = fma2(complement, a, ga);
+    uint64_t const raw = mul2(complement, scale);
+    coefficient = fma2(raw, prefix_dot, coefficient);
     return raw;
 }
 
@@ -156,22 +179,26 @@ __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::
 
 // ---- roles ------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensorMap const* c_map, fwd_params const& p,
-                                              uint32_t stages_base, fwd_tail* tail, wait_context const& ctx) {
+                                              uint32_t stages_base, fwd_tail* tail, wait_context const& ctx,
+                                              uint32_t const stages) {
     uint32_t stage = 0, phase = 0;
     uint32_t const chunks = p.hidden / fwd_depth;
+    long long clock = clock64();
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t const column_tile = run * p.tiles_per_run + t;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
+                trace_phase(p, 0, clock);
                 if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
+                trace_phase(p, 1, clock);
                 uint32_t const full = smem_u32(&tail->stage_full[stage]);
                 uint32_t const destination = stages_base + stage * fwd_stage_bytes;
                 mbar_arrive_expect_tx(full, fwd_stage_bytes);
                 tma_load_2d(destination, q_map, full, chunk * static_cast<int>(fwd_depth), static_cast<int>(strip * fwd_rows));
                 tma_load_2d(destination + fwd_q_bytes, c_map, full, chunk * static_cast<int>(fwd_depth),
                             static_cast<int>(column_tile * fwd_cols));
-                if (++stage == fwd_stages) stage = 0, phase ^= 1u;
+                if (++stage == stages) stage = 0, phase ^= 1u;
             }
         }
     }
@@ -201,19 +228,24 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     }
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
     uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0;
+    long long clock = clock64();
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t slot_address = 0, accumulate = 0;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
                 uint32_t const starts = tail->band_starts[chunk];
+                trace_phase(p, 2, clock);
                 if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
+                trace_phase(p, 3, clock);
                 tcgen05_fence_after();
                 uint32_t const low = low_base + stage * (fwd_stage_bytes >> 4);
 #pragma unroll
                 for (int sub = 3; sub >= 0; --sub) {
                     if ((starts >> (8 * sub)) & 0xFFu) {
                         uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
+                        trace_phase(p, 2, clock);
                         if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
+                        trace_phase(p, 4, clock);
                         tcgen05_fence_after();
                         slot_address = tmem_base + slot * fwd_slot_columns;
                         accumulate = 0;
@@ -227,7 +259,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
                     accumulate = 1;
                 }
                 umma_commit(smem_u32(&tail->stage_empty[stage]));
-                if (++stage == fwd_stages) stage = 0, phase ^= 1u;
+                if (++stage == fwd_stages_for(prefixes_)) stage = 0, phase ^= 1u;
             }
             umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
             ++tile_local;
@@ -252,7 +284,8 @@ struct tile_cursor {
 // segment dots come out of tensor memory, its raw-dot gradients go back into the same slot, and a second rolled pass
 // reads them widest first to form the suffix sums. Per-thread sums that are indexed by prefix live in shared memory.
 template <int prefixes_>
-__device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tail, float* norm_staging, float* thread_state,
+__device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_params const& p, fwd_tail* tail,
+                                              uint32_t store_base, float* norm_staging, float* thread_state,
                                               uint32_t tmem_base, wait_context const& ctx, uint32_t warp, uint32_t lane) {
     constexpr int columns = fwd_chunk_columns;
     constexpr int norm_count = prefixes_ * columns;
@@ -268,7 +301,7 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
     float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][8][16]
     float* const staged_max = staged_norms + 2 * 8 * columns;                   // [2][8]
     float* const mine = thread_state + threadIdx.x;                             // [3 * prefixes_] strided by the thread count
-    uint32_t tile_local = 0, buffer = 0;
+    uint32_t tile_local = 0, buffer = 0, store_buffer = 0;
 
     tile_cursor cursor{blockIdx.x, 0};
     if (!cursor.valid(p)) return;
@@ -301,6 +334,7 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
     float g = 0.0f, ga = 0.0f;
     uint32_t row = 0;
     uint64_t global_row = 0;
+    long long epilogue_clock = clock64();
 
     while (cursor.valid(p)) {
         tile_cursor const following = cursor.next(p);
@@ -329,37 +363,54 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
         for (int k = 0; k < prefixes_; ++k) special |= mine[k * fwd_epilogue_threads] * staged_max[buffer * 8 + k] >= 100.0f;
         special = __any_sync(0xFFFFFFFFu, special);
 
+        if (threadIdx.x == 0) trace_phase(p, 5, epilogue_clock);
         if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u, ctx,
                        site_fwd_tile_full, tile_local))
             return;
         tcgen05_fence_after();
+        if (threadIdx.x == 0) trace_phase(p, 6, epilogue_clock);
 
         uint32_t const first_unit = tile_local * prefixes_;
-        float prefix[columns];
+        uint64_t prefix[columns / 2];
 #pragma unroll
-        for (int c = 0; c < columns; ++c) prefix[c] = 0.0f;
+        for (int c = 0; c < columns / 2; ++c) prefix[c] = 0ull;
+        uint64_t const bias2 = pack2(bias, bias);
 #pragma unroll 1
         for (int k = 0; k < prefixes_; ++k) {
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
             uint32_t d[columns];
             tmem_load_16(address, d);
-            float inv_c[columns];
-            float4 const* source = reinterpret_cast<float4 const*>(norms_now + k * columns);
+            uint64_t inv_c[columns / 2];
+            ulonglong2 const* source = reinterpret_cast<ulonglong2 const*>(norms_now + k * columns);
 #pragma unroll
             for (int v = 0; v < columns / 4; ++v) {
-                float4 const four = source[v];
-                inv_c[4 * v] = four.x, inv_c[4 * v + 1] = four.y, inv_c[4 * v + 2] = four.z, inv_c[4 * v + 3] = four.w;
+                ulonglong2 const four = source[v];
+                inv_c[2 * v] = four.x, inv_c[2 * v + 1] = four.y;
             }
             float const inv_q = mine[k * fwd_epilogue_threads];
             float const row_beta = beta * inv_q;
             float loss = 0.0f, coefficient = 0.0f;
             tmem_load_wait();
             if (!special) {
+                uint64_t const row_beta2 = pack2(row_beta, row_beta);
+                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull, ga2 = 0ull;
 #pragma unroll
-                for (int c = 0; c < columns; ++c) {
-                    prefix[c] += __uint_as_float(d[c]);
-                    d[c] = __float_as_uint(cell_fast(prefix[c], inv_c[c], row_beta, bias, loss, g, ga, coefficient));
+                for (int c = 0; c < columns / 2; ++c) {
+                    prefix[c] = add2(prefix[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
+                    uint64_t const raw = cell_fast2(prefix[c], inv_c[c], row_beta2, bias2, loss2, g2, ga2, coefficient2);
+                    float raw0, raw1;
+                    unpack2(raw, raw0, raw1);
+                    d[2 * c] = __float_as_uint(raw0), d[2 * c + 1] = __float_as_uint(raw1);
                 }
+                float lo, hi;
+                unpack2(loss2, lo, hi);
+                loss = lo + hi;
+                unpack2(coefficient2, lo, hi);
+                coefficient = lo + hi;
+                unpack2(g2, lo, hi);
+                g += lo + hi;
+                unpack2(ga2, lo, hi);
+                ga += lo + hi;
             } else {
                 // Which of this warp's 16 columns, if any, is the row's own copy or its pair partner.
                 int64_t const first = static_cast<int64_t>(p.candidate_base + column);
@@ -369,10 +420,15 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
                 int const partner_column =
                     (p.spec_code & 1u) != 0u && partner_at >= 0 && partner_at < columns ? static_cast<int>(partner_at) : -1;
 #pragma unroll
-                for (int c = 0; c < columns; ++c) {
-                    prefix[c] += __uint_as_float(d[c]);
-                    d[c] = __float_as_uint(cell_general(prefix[c], inv_q, inv_c[c], constants, c == own_column,
-                                                        c == partner_column, p.spec_code, loss, g, ga, coefficient));
+                for (int c = 0; c < columns / 2; ++c) {
+                    prefix[c] = add2(prefix[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
+                    float dot0, dot1, norm0, norm1;
+                    unpack2(prefix[c], dot0, dot1);
+                    unpack2(inv_c[c], norm0, norm1);
+                    d[2 * c] = __float_as_uint(cell_general(dot0, inv_q, norm0, constants, 2 * c == own_column,
+                                                            2 * c == partner_column, p.spec_code, loss, g, ga, coefficient));
+                    d[2 * c + 1] = __float_as_uint(cell_general(dot1, inv_q, norm1, constants, 2 * c + 1 == own_column,
+                                                                2 * c + 1 == partner_column, p.spec_code, loss, g, ga, coefficient));
                 }
             }
             tmem_store_16(address, d);
@@ -380,10 +436,11 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
             mine[(2 * prefixes_ + k) * fwd_epilogue_threads] += coefficient;
         }
         tmem_store_wait();
+        if (threadIdx.x == 0) trace_phase(p, 7, epilogue_clock);
         // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
-        float running[columns];
+        uint64_t running[columns / 2];
 #pragma unroll
-        for (int c = 0; c < columns; ++c) running[c] = 0.0f;
+        for (int c = 0; c < columns / 2; ++c) running[c] = 0ull;
 #pragma unroll 1
         for (int k = prefixes_ - 1; k >= 0; --k) {
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
@@ -392,15 +449,35 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
             tmem_load_wait();
             uint32_t packed[columns / 2];
 #pragma unroll
-            for (int c = 0; c < columns; c += 2) {
-                running[c] += __uint_as_float(d[c]);
-                running[c + 1] += __uint_as_float(d[c + 1]);
-                packed[c / 2] = pack_bf16x2(running[c], running[c + 1]);
+            for (int c = 0; c < columns / 2; ++c) {
+                running[c] = add2(running[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
+                float lo, hi;
+                unpack2(running[c], lo, hi);
+                packed[c] = pack_bf16x2(lo, hi);
             }
-            uint4* destination = reinterpret_cast<uint4*>(p.cube + (static_cast<size_t>(k) * p.rows_q + row) * p.rows_c + column);
-            destination[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            destination[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            // The warp's [32 rows x 16 columns] patch of the band goes to the warp's own staging buffer (32 bytes per row)
+            // and leaves as a TMA store issued by lane 0, so no load/store-unit instruction touches global memory and no
+            // other warp is waited for. Two buffers alternate: before a buffer is rewritten, the store that read it two
+            // bands ago must have finished reading.
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]), "r"(packed[1]),
+                         "r"(packed[2]), "r"(packed[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u + 16u), "r"(packed[4]),
+                         "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(cube_map)),
+                             "r"(patch), "r"(column), "r"(strip * fwd_rows + quadrant * 32u), "r"(k)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            store_buffer ^= 1u;
         }
+        if (threadIdx.x == 0) trace_phase(p, 8, epilogue_clock);
         // This warp is done with the tile's slots.
         tcgen05_fence_before();
         __syncwarp();
@@ -426,6 +503,8 @@ __device__ __forceinline__ void epilogue_role(fwd_params const& p, fwd_tail* tai
         buffer ^= 1u;
         ++tile_local;
     }
+    // The staging buffers must outlive the stores that read them.
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void pull_role(pull_request const& request, uint32_t thread_in_role) {
@@ -450,16 +529,19 @@ __device__ __forceinline__ void pull_role(pull_request const& request, uint32_t 
 
 template <int prefixes_>
 __global__ void __launch_bounds__(fwd_threads, 1)
-    forward_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap c_map, const fwd_params p) {
+    forward_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap c_map,
+                   const __grid_constant__ CUtensorMap cube_map, const fwd_params p) {
     extern __shared__ uint8_t raw_shared[];
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
-    fwd_tail* tail = reinterpret_cast<fwd_tail*>(raw_shared + (stages_base - raw_address) + fwd_stages * fwd_stage_bytes);
+    fwd_tail* tail =
+        reinterpret_cast<fwd_tail*>(raw_shared + (stages_base - raw_address) + fwd_stages_for(prefixes_) * fwd_stage_bytes +
+                                    fwd_store_bytes);
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
         tail->abort_flag = status_poisoned(p.status) ? 1u : 0u;
-        for (uint32_t i = 0; i < fwd_stages; ++i) {
+        for (uint32_t i = 0; i < fwd_max_stages; ++i) {
             mbar_init(smem_u32(&tail->stage_full[i]), 1);
             mbar_init(smem_u32(&tail->stage_empty[i]), 1);
         }
@@ -485,9 +567,10 @@ __global__ void __launch_bounds__(fwd_threads, 1)
 
     if (warp < fwd_epilogue_warps) {
         float* const norm_staging = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + fwd_tail_bytes);
-        epilogue_role<prefixes_>(p, tail, norm_staging, norm_staging + fwd_norm_bytes / 4, tmem_base, ctx, warp, lane);
+        epilogue_role<prefixes_>(&cube_map, p, tail, stages_base + fwd_stages_for(prefixes_) * fwd_stage_bytes, norm_staging,
+                                 norm_staging + fwd_norm_bytes / 4, tmem_base, ctx, warp, lane);
     } else if (warp == fwd_producer_warp) {
-        if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx);
+        if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx, fwd_stages_for(prefixes_));
     } else if (warp == fwd_mma_warp) {
         if (lane == 0) mma_role<prefixes_>(p, stages_base, tail, tmem_base, ctx);
     } else {
@@ -523,11 +606,12 @@ CUtensorMap make_map_2d(void const* base, uint64_t inner, uint64_t outer, uint32
 }
 
 template <int prefixes_>
-void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, fwd_params const& p, int blocks, cudaStream_t stream) {
+void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, CUtensorMap const& cube_map, fwd_params const& p,
+                     int blocks, cudaStream_t stream) {
     require(cudaFuncSetAttribute(forward_kernel<prefixes_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fwd_shared_bytes(prefixes_)),
             "raising the forward kernel's shared memory");
-    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes(prefixes_), stream>>>(q_map, c_map, p);
+    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes(prefixes_), stream>>>(q_map, c_map, cube_map, p);
 }
 
 } // namespace
@@ -570,21 +654,32 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     p.query_base = a.query_base, p.candidate_base = a.candidate_base, p.spec_code = a.spec_code;
     p.budget_ns = a.budget_ns;
     p.pull = a.pull;
+    p.trace = a.trace;
 
     CUtensorMap const q_map = make_map_2d(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
     CUtensorMap const c_map = make_map_2d(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
+    CUtensorMap cube_map;
+    {
+        cuuint64_t const dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
+        cuuint64_t const strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
+        cuuint32_t const box[3] = {fwd_chunk_columns, 32, 1};
+        cuuint32_t const element_strides[3] = {1, 1, 1};
+        SC_DRIVER(cuTensorMapEncodeTiled, &cube_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.gradient_cube_bf16, dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     int blocks = static_cast<int>(p.items < static_cast<uint32_t>(a.multiprocessors) ? p.items : a.multiprocessors);
     if ((a.pull.bytes[0] | a.pull.bytes[1]) != 0 && blocks < a.multiprocessors / 2) blocks = a.multiprocessors / 2;
     if (blocks < 1) blocks = 1;
     switch (a.ladder.count) {
-    case 1: launch_instance<1>(q_map, c_map, p, blocks, stream); break;
-    case 2: launch_instance<2>(q_map, c_map, p, blocks, stream); break;
-    case 3: launch_instance<3>(q_map, c_map, p, blocks, stream); break;
-    case 4: launch_instance<4>(q_map, c_map, p, blocks, stream); break;
-    case 5: launch_instance<5>(q_map, c_map, p, blocks, stream); break;
-    case 6: launch_instance<6>(q_map, c_map, p, blocks, stream); break;
-    case 7: launch_instance<7>(q_map, c_map, p, blocks, stream); break;
-    default: launch_instance<8>(q_map, c_map, p, blocks, stream); break;
+    case 1: launch_instance<1>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 2: launch_instance<2>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 3: launch_instance<3>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 4: launch_instance<4>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 5: launch_instance<5>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 6: launch_instance<6>(q_map, c_map, cube_map, p, blocks, stream); break;
+    case 7: launch_instance<7>(q_map, c_map, cube_map, p, blocks, stream); break;
+    default: launch_instance<8>(q_map, c_map, cube_map, p, blocks, stream); break;
     }
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("forward launch failed: ") + cudaGetErrorString(error));
