@@ -86,6 +86,9 @@ def main() -> int:
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL only carries the barrier and the max-over-ranks here; keep it off the switch's multicast resources, which
+        # the library's own domain binds.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
     ext = _ext.native()  # raises when the extension is missing: no silent fallback
 

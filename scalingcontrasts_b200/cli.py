@@ -173,6 +173,7 @@ class RankContext:
         if self.world > 1 and not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             if self.cuda:
+                os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # NCCL is bootstrap only; the domain owns the multicast
                 dist.init_process_group("nccl", device_id=self.device)
             else:
                 dist.init_process_group("gloo")

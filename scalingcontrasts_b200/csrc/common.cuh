@@ -283,17 +283,23 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
-// log1p(x) / x for both halves of a pair (the same polynomial as log1p_ratio).
+// log1p(x) / x for both halves of a pair (the same polynomial as log1p_ratio). The coefficients sit in constant memory
+// already duplicated into pairs, so that they can be operands of the packed instructions without register pairs of
+// their own.
+__constant__ float2 log1p_pairs[9] = {{SC_LOG1P_C0, SC_LOG1P_C0}, {SC_LOG1P_C1, SC_LOG1P_C1}, {SC_LOG1P_C2, SC_LOG1P_C2},
+                                      {SC_LOG1P_C3, SC_LOG1P_C3}, {SC_LOG1P_C4, SC_LOG1P_C4}, {SC_LOG1P_C5, SC_LOG1P_C5},
+                                      {SC_LOG1P_C6, SC_LOG1P_C6}, {SC_LOG1P_C7, SC_LOG1P_C7}, {SC_LOG1P_C8, SC_LOG1P_C8}};
+__device__ __forceinline__ uint64_t log1p_pair(int index) { return *reinterpret_cast<uint64_t const*>(&log1p_pairs[index]); }
 __device__ __forceinline__ uint64_t log1p_ratio2(uint64_t x) {
-    uint64_t p = pack2(SC_LOG1P_C8, SC_LOG1P_C8);
-    p = fma2(p, x, pack2(SC_LOG1P_C7, SC_LOG1P_C7));
-    p = fma2(p, x, pack2(SC_LOG1P_C6, SC_LOG1P_C6));
-    p = fma2(p, x, pack2(SC_LOG1P_C5, SC_LOG1P_C5));
-    p = fma2(p, x, pack2(SC_LOG1P_C4, SC_LOG1P_C4));
-    p = fma2(p, x, pack2(SC_LOG1P_C3, SC_LOG1P_C3));
-    p = fma2(p, x, pack2(SC_LOG1P_C2, SC_LOG1P_C2));
-    p = fma2(p, x, pack2(SC_LOG1P_C1, SC_LOG1P_C1));
-    return fma2(p, x, pack2(SC_LOG1P_C0, SC_LOG1P_C0));
+    uint64_t p = log1p_pair(8);
+    p = fma2(p, x, log1p_pair(7));
+    p = fma2(p, x, log1p_pair(6));
+    p = fma2(p, x, log1p_pair(5));
+    p = fma2(p, x, log1p_pair(4));
+    p = fma2(p, x, log1p_pair(3));
+    p = fma2(p, x, log1p_pair(2));
+    p = fma2(p, x, log1p_pair(1));
+    return fma2(p, x, log1p_pair(0));
 }
 
 // Matryoshka ladder by value, the form kernels take (ascending ends, zero padded).

@@ -39,7 +39,7 @@ constexpr uint32_t fwd_cols = 64;
 constexpr uint32_t fwd_depth = 64;
 constexpr uint32_t fwd_max_stages = 6;
 // Ladders of up to five prefixes leave room for six stages; longer ones keep more per-thread state and get five.
-constexpr uint32_t fwd_stages_for(uint32_t prefixes) { return prefixes <= 5 ? 6u : 5u; }
+__host__ __device__ constexpr uint32_t fwd_stages_for(uint32_t prefixes) { return prefixes <= 5 ? 6u : 5u; }
 constexpr uint32_t fwd_slots = 8;
 constexpr uint32_t fwd_slot_columns = 64;
 constexpr uint32_t fwd_tmem_columns = 512;
@@ -71,12 +71,12 @@ constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
 constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_chunk_columns + 8);
 constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
 // Per epilogue thread: inverse norm, loss and coefficient of every prefix, laid out [3 * prefixes][thread].
-constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
+__host__ __device__ constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
 // Per epilogue warp two staging buffers of [32 rows][16 columns] bfloat16, from which the warp's patch of a band's
 // gradient cube leaves through a TMA store while the next band is being computed.
 constexpr uint32_t fwd_store_patch_bytes = 32 * fwd_chunk_columns * 2;
 constexpr uint32_t fwd_store_bytes = fwd_epilogue_warps * 2 * fwd_store_patch_bytes;
-constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
+__host__ __device__ constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
     return 1024 + fwd_stages_for(prefixes) * fwd_stage_bytes + fwd_store_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
 }
 
@@ -380,13 +380,9 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
             uint32_t d[columns];
             tmem_load_16(address, d);
-            uint64_t inv_c[columns / 2];
-            ulonglong2 const* source = reinterpret_cast<ulonglong2 const*>(norms_now + k * columns);
-#pragma unroll
-            for (int v = 0; v < columns / 4; ++v) {
-                ulonglong2 const four = source[v];
-                inv_c[2 * v] = four.x, inv_c[2 * v + 1] = four.y;
-            }
+            // Candidate norms are read from the warp's staging buffer pair by pair, right where they are used (broadcast
+            // shared loads), which keeps sixteen registers free for interleaving the cells.
+            uint64_t const* const inv_c = reinterpret_cast<uint64_t const*>(norms_now + k * columns);
             float const inv_q = mine[k * fwd_epilogue_threads];
             float const row_beta = beta * inv_q;
             float loss = 0.0f, coefficient = 0.0f;
