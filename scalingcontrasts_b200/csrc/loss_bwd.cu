@@ -5,6 +5,9 @@
 // so its A operand is a single band's cube. Candidates arrive transposed ([H, R], K-major rows of candidates), the
 // cube through a three-dimensional TMA map.
 //
+// A CTA owns one or two 128-row blocks of a strip (two when there are enough strips to fill the GPU): both blocks use
+// the same candidate stage, which halves the candidate refills from L2, the traffic this kernel is bound by.
+//
 // Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lanes 32*w..), warp 4 TMA producer, warp 5 UMMA issuer
 // and tensor-memory owner. With `split == 1` each output element is touched by exactly one CTA per launch (plain
 // read-modify-write, deterministic); with a larger split the candidate range is divided and partial sums are added
@@ -25,11 +28,12 @@ namespace {
 constexpr uint32_t bwd_rows = 128;
 constexpr uint32_t bwd_depth = 64;        // candidates per stage
 constexpr uint32_t bwd_max_width = 192;   // channels per tile
-constexpr uint32_t bwd_stages = 4;
-constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;
+constexpr uint32_t bwd_stages = 4;                                  // with one row block per CTA; three with two
+constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;        // one 128-row block of the cube
 constexpr uint32_t bwd_b_bytes = bwd_max_width * bwd_depth * 2;
-constexpr uint32_t bwd_stage_bytes = bwd_a_bytes + bwd_b_bytes;
-constexpr uint32_t bwd_tmem_columns = 256;
+constexpr uint32_t bwd_stage_bytes = 2 * bwd_a_bytes + bwd_b_bytes; // up to two row blocks share one candidate tile
+constexpr uint32_t bwd_tmem_columns = 512;
+constexpr uint32_t bwd_block_columns = 256;                         // tensor-memory columns between the two accumulators
 constexpr uint32_t bwd_threads = 192;
 constexpr uint32_t bwd_max_tiles = 32;
 
@@ -40,7 +44,7 @@ struct bwd_tail {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-constexpr uint32_t bwd_shared_bytes = 1024 + bwd_stages * bwd_stage_bytes + sizeof(bwd_tail);
+constexpr uint32_t bwd_shared_bytes = 1024 + 3 * bwd_stage_bytes + sizeof(bwd_tail); // >= 4 * (one block + candidates)
 
 struct bwd_tile {
     uint32_t band, channel0, width;
@@ -51,6 +55,7 @@ struct bwd_params {
     uint32_t* status;
     uint32_t rows_q, rows_c, hidden;
     uint32_t tile_count, split;
+    uint32_t blocks_per_cta; // 1 or 2 row blocks of 128
     float scale; // applied to every product before it is added: the loss's 2/N (mirror cell and weight)
     uint64_t budget_ns;
     bwd_tile tiles[bwd_max_tiles];
@@ -62,10 +67,15 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     extern __shared__ uint8_t raw_shared[];
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
-    bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + bwd_stages * bwd_stage_bytes);
+    bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + 3 * bwd_stage_bytes);
+    // Stage geometry: [row blocks of the cube][candidate tile]; four stages of 40 KB or three of 56 KB.
+    uint32_t const stage_bytes = p.blocks_per_cta * bwd_a_bytes + bwd_b_bytes;
+    uint32_t const stages = p.blocks_per_cta == 2 ? 3u : 4u;
+    uint32_t const b_offset = p.blocks_per_cta * bwd_a_bytes;
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     bwd_tile const tile = p.tiles[blockIdx.x];
-    uint32_t const strip = blockIdx.y;
+    uint32_t const first_block = blockIdx.y * p.blocks_per_cta;
+    uint32_t const blocks = min(p.blocks_per_cta, p.rows_q / bwd_rows - first_block);
     uint32_t const chunks_total = p.rows_c / bwd_depth;
     uint32_t const chunks_per_split = (chunks_total + p.split - 1) / p.split;
     uint32_t const chunk_begin = min(blockIdx.z * chunks_per_split, chunks_total);
@@ -99,18 +109,19 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     if (warp == 4) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
-            uint32_t const bytes = bwd_a_bytes + tile.width * bwd_depth * 2;
+            uint32_t const bytes = blocks * bwd_a_bytes + tile.width * bwd_depth * 2;
             for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
                 if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_bwd_stage_empty, chunk)) break;
                 uint32_t const full = smem_u32(&tail->stage_full[stage]);
-                uint32_t const destination = stages_base + stage * bwd_stage_bytes;
+                uint32_t const destination = stages_base + stage * stage_bytes;
                 mbar_arrive_expect_tx(full, bytes);
-                tma_load_3d(destination, &cube_map, full, static_cast<int>(chunk * bwd_depth), static_cast<int>(strip * bwd_rows),
-                            static_cast<int>(tile.band));
+                for (uint32_t block = 0; block < blocks; ++block)
+                    tma_load_3d(destination + block * bwd_a_bytes, &cube_map, full, static_cast<int>(chunk * bwd_depth),
+                                static_cast<int>((first_block + block) * bwd_rows), static_cast<int>(tile.band));
                 for (uint32_t r = 0; r < tile.width / 16; ++r)
-                    tma_load_2d(destination + bwd_a_bytes + r * 2048u, &candidates_map, full, static_cast<int>(chunk * bwd_depth),
-                                static_cast<int>(tile.channel0 + r * 16));
-                if (++stage == bwd_stages) stage = 0, phase ^= 1u;
+                    tma_load_2d(destination + b_offset + r * 2048u, &candidates_map, full,
+                                static_cast<int>(chunk * bwd_depth), static_cast<int>(tile.channel0 + r * 16));
+                if (++stage == stages) stage = 0, phase ^= 1u;
             }
         }
     } else if (warp == 5) {
@@ -122,24 +133,28 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                 ok = mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_bwd_stage_full, chunk);
                 if (!ok) break;
                 tcgen05_fence_after();
-                uint32_t const a_address = stages_base + stage * bwd_stage_bytes;
+                uint32_t const a_address = stages_base + stage * stage_bytes;
+                for (uint32_t block = 0; block < blocks; ++block) {
 #pragma unroll
-                for (uint32_t step = 0; step < bwd_depth / 16; ++step) {
-                    umma_bf16(tmem_base, umma_desc_k_major_sw128(a_address + step * 32u, 1024u),
-                              umma_desc_k_major_sw128(a_address + bwd_a_bytes + step * 32u, 1024u), idesc, accumulate);
-                    accumulate = 1;
+                    for (uint32_t step = 0; step < bwd_depth / 16; ++step)
+                        umma_bf16(tmem_base + block * bwd_block_columns,
+                                  umma_desc_k_major_sw128(a_address + block * bwd_a_bytes + step * 32u, 1024u),
+                                  umma_desc_k_major_sw128(a_address + b_offset + step * 32u, 1024u), idesc,
+                                  step == 0 ? accumulate : 1u);
                 }
+                accumulate = 1;
                 umma_commit(smem_u32(&tail->stage_empty[stage]));
-                if (++stage == bwd_stages) stage = 0, phase ^= 1u;
+                if (++stage == stages) stage = 0, phase ^= 1u;
             }
             if (ok) umma_commit(smem_u32(&tail->accumulated));
         }
     } else {
         if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.x)) {
             tcgen05_fence_after();
-            uint32_t const row = strip * bwd_rows + warp * 32 + lane;
+          for (uint32_t block = 0; block < blocks; ++block) {
+            uint32_t const row = (first_block + block) * bwd_rows + warp * 32 + lane;
             float* destination = p.query_gradient + static_cast<size_t>(row) * p.hidden + tile.channel0;
-            uint32_t const lane_base = tmem_base + ((warp * 32u) << 16);
+            uint32_t const lane_base = tmem_base + ((warp * 32u) << 16) + block * bwd_block_columns;
             for (uint32_t column = 0; column < tile.width; column += 16) {
                 uint32_t values[16];
                 tmem_load_16(lane_base + column, values);
@@ -160,6 +175,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                     for (int c = 0; c < 16; ++c) atomicAdd(destination + column + c, p.scale * __uint_as_float(values[c]));
                 }
             }
+          }
         }
     }
 
@@ -217,7 +233,13 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
 
     require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
             "raising the backward kernel's shared memory");
-    dim3 const grid(p.tile_count, a.rows_q / bwd_rows, a.split);
+    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor.
+    int device = 0, multiprocessors = 148;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
+    uint32_t const row_blocks = a.rows_q / bwd_rows;
+    p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
+    dim3 const grid(p.tile_count, (row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, a.split);
     backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates_map, p);
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("backward launch failed: ") + cudaGetErrorString(error));
