@@ -10,8 +10,8 @@
 Rows keep the reference's leading columns so that they paste into the same tables, with device-timed columns added at
 the end:
 
-    simulate,R,H,K,S,bytes,min_ms,median_ms,gcells_per_s
-    box|hosts,R,H,K,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu
+    simulate,R,H,K,S,bytes,min_ms,median_ms,gcells_per_s,roofline_ms,fraction_of_roofline,peaks
+    box|hosts,R,H,K,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks
     oracle,R,H,K,ranks,exact_loss,measured_loss,rel_grad_err,disagreeing
     barrier,count,stride,min_us,median_us
     reduce_scatter|all_reduce,count,bytes,min_us,median_us,algbw,busbw
@@ -143,9 +143,9 @@ def run(argv: List[str]) -> None:
 
 
 HEADERS = {
-    "simulate": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s",
-    "box": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu",
-    "hosts": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu",
+    "simulate": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s,roofline_ms,fraction_of_roofline,peaks",
+    "box": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks",
+    "hosts": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks",
     "oracle": "mode,rows,hidden,prefixes,ranks,exact_loss,measured_loss,rel_grad_err,disagreeing",
     "collectives": "mode,count,bytes,min_us,median_us,algbw,busbw",
     "train": "mode,rows,hidden,prefixes,world,min_ms,median_ms,gcells_per_s",
@@ -219,6 +219,16 @@ def _box_engine(context: RankContext):
     return BoxLoss(s.rows, s.hidden, ladder, s.spec(), domain), domain
 
 
+def _roofline_columns(rows: int, world: int, hidden: int, min_ms: float) -> str:
+    """``roofline_ms,fraction,source``: the step's bound (tensor time at the measured peak, or peer pulls at link
+    bandwidth, whichever is slower) and how much of it the measured time reaches."""
+    from .utils.roofline import load_peaks, loss_step_roofline_ms
+
+    peaks = load_peaks()
+    bound = loss_step_roofline_ms(rows, world, hidden, peaks)
+    return f"{bound:.4f},{bound / min_ms:.3f},{peaks.source}"
+
+
 def _time(context: RankContext, step, windows: int, calls: int):
     from .utils.timing import time_windows
 
@@ -244,7 +254,7 @@ def run_simulate(context: RankContext) -> None:
     engine.check()
     cells = s.rows * s.rows * world * ladder.count
     context.emit(f"simulate,{s.rows},{s.hidden},{ladder.count},{world},{engine.bytes()},{timing.min_ms:.4f},"
-                 f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f}")
+                 f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f},{_roofline_columns(s.rows, world, s.hidden, timing.min_ms)}")
 
 
 def run_box(context: RankContext) -> None:
@@ -258,7 +268,8 @@ def run_box(context: RankContext) -> None:
     engine.check()
     cells = s.rows * s.rows * context.world * engine.ladder.count
     context.emit(f"box,{s.rows},{s.hidden},{engine.ladder.count},{context.world},{engine.bytes()},{timing.min_ms:.4f},"
-                 f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f}")
+                 f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f},"
+                 f"{_roofline_columns(s.rows, context.world, s.hidden, timing.min_ms)}")
     domain.close()
 
 

@@ -117,10 +117,10 @@ struct row_constants {
 
 // A negative cell whose cosine is off the floor has z = -1 and s = -(logit + bias). The fast path handles two such cells
 // at once on packed pairs and returns their gradients with respect to the raw dot product WITHOUT the factor 2/N (mirror
-// cell and weight), which the backward kernel applies once per element. `loss`, `g`, `ga` and `coefficient` are pairs of
-// partial sums whose halves are added when the band is done.
+// cell and weight), which the backward kernel applies once per element. `loss`, `g` and `coefficient` are pairs of partial
+// sums whose halves are added when the band is done.
 __device__ __forceinline__ uint64_t cell_fast2(uint64_t prefix_dot, uint64_t inv_c, uint64_t row_beta, uint64_t bias,
-                                               uint64_t& loss, uint64_t& g, uint64_t& ga, uint64_t& coefficient) {
+                                               uint64_t& loss, uint64_t& g, uint64_t& coefficient) {
     uint64_t const scale = mul2(inv_c, row_beta);
     uint64_t const a = fma2(prefix_dot, scale, bias);
     float a0, a1;
@@ -134,7 +134,6 @@ __device__ __forceinline__ uint64_t cell_fast2(uint64_t prefix_dot, uint64_t inv
     loss = add2(loss, pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
     loss = fma2(log1p_ratio2(e), e, loss);
     g = add2(g, complement);
-    ga = fma2(complement, a, ga);
     uint64_t const raw = mul2(complement, scale);
     coefficient = fma2(raw, prefix_dot, coefficient);
     return raw;
@@ -389,24 +388,25 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             tmem_load_wait();
             if (!special) {
                 uint64_t const row_beta2 = pack2(row_beta, row_beta);
-                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull, ga2 = 0ull;
+                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull;
 #pragma unroll
                 for (int c = 0; c < columns / 2; ++c) {
                     prefix[c] = add2(prefix[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
-                    uint64_t const raw = cell_fast2(prefix[c], inv_c[c], row_beta2, bias2, loss2, g2, ga2, coefficient2);
+                    uint64_t const raw = cell_fast2(prefix[c], inv_c[c], row_beta2, bias2, loss2, g2, coefficient2);
                     float raw0, raw1;
                     unpack2(raw, raw0, raw1);
                     d[2 * c] = __float_as_uint(raw0), d[2 * c + 1] = __float_as_uint(raw1);
                 }
-                float lo, hi;
+                float lo, hi, band_g;
                 unpack2(loss2, lo, hi);
                 loss = lo + hi;
                 unpack2(coefficient2, lo, hi);
                 coefficient = lo + hi;
                 unpack2(g2, lo, hi);
-                g += lo + hi;
-                unpack2(ga2, lo, hi);
-                ga += lo + hi;
+                band_g = lo + hi;
+                g += band_g;
+                // sum of complement * (logit + bias) = sum of raw * dot + bias * sum of complement
+                ga += fmaf(bias, band_g, coefficient);
             } else {
                 // Which of this warp's 16 columns, if any, is the row's own copy or its pair partner.
                 int64_t const first = static_cast<int64_t>(p.candidate_base + column);

@@ -21,7 +21,7 @@ from typing import Optional
 import torch
 from torch import nn
 
-from ..config import DEFAULT_BETA, DEFAULT_BIAS, LossSpec, REFERENCE_SPEC
+from ..config import DEFAULT_BETA, DEFAULT_BIAS, LossSpec, REFERENCE_SPEC, SUMMAND_SLOTS
 from ..ladder import Matryoshka
 
 
@@ -70,12 +70,14 @@ class _HostLoss(torch.autograd.Function):
         else:
             blocks = [block]
         beta, bias = float(logit_scale.detach().exp()), float(logit_bias.detach())
-        loss = CpuStreamedLoss(rows, hidden, module.ladder, module.spec, torch.float32)
+        precision = torch.float64 if block.dtype == torch.float64 else torch.float32
+        loss = CpuStreamedLoss(rows, hidden, module.ladder, module.spec, precision)
         loss.begin(block)
         for p in range(world):
             peer = (rank + p) % world
             loss.score(block, blocks[peer], rank * rows, peer * rows, beta, bias, world * rows)
-        gradient, summands = loss.finish(block, torch.empty(rows, hidden, dtype=torch.float32))
+        gradient, summands = loss.finish(block, torch.empty(rows, hidden, dtype=precision),
+                                         torch.zeros(SUMMAND_SLOTS, dtype=precision))
         if world > 1:
             dist.all_reduce(summands, op=dist.ReduceOp.SUM, group=module.group)
         ctx.save_for_backward(gradient, summands)

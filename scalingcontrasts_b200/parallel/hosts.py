@@ -194,8 +194,11 @@ def run_hosts_mode(context) -> None:
         timing = time_windows(lambda: engine.step(block, s.beta, s.bias), s.windows, 3, context.device)
         engine.check()
         cells = s.rows * s.rows * context.world * ladder.count
+        from ..cli import _roofline_columns
+
         context.emit(f"hosts,{s.rows},{s.hidden},{ladder.count},{context.world},{engine.bytes()},{timing.min_ms:.4f},"
-                     f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f}")
+                     f"{timing.median_ms:.4f},{cells / timing.min_ms / 1e6:.1f},"
+                     f"{_roofline_columns(s.rows, context.world, s.hidden, timing.min_ms)}")
     context.barrier()
     engine.close()
     domain.close()
