@@ -38,7 +38,8 @@ def test_prefix_norms_transpose_and_keyed_generator(ext):
     assert torch.equal(out, block.T.contiguous())
 
 
-@pytest.mark.parametrize("rows,hidden,prefixes", [(128, 64, 1), (128, 256, 3), (256, 768, 5), (128, 2048, 8)])
+@pytest.mark.parametrize("rows,hidden,prefixes", [(128, 64, 1), (128, 128, 2), (128, 256, 3), (256, 1024, 4), (256, 768, 5),
+                                                  (128, 1024, 6), (128, 1024, 7), (128, 2048, 8)])
 def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefixes):
     """The forward kernel's per-band gradient cubes and the backward kernel's fold, each checked on its own."""
     _float32_matmul_exact()
