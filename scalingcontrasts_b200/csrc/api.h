@@ -113,7 +113,7 @@ struct forward_arguments {
     unsigned long long* trace;
     int multiprocessors;
 };
-// Returns the number of partial slots the launch fills: 4 * rows_c / 64 / tiles_per_run.
+// Returns the number of partial slots the launch fills: (column groups per tile) * rows_c / 64 / tiles_per_run.
 uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run);
 uint32_t forward_quantities(uint32_t prefixes);
 uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors);

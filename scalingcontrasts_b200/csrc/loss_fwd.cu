@@ -43,12 +43,18 @@ __host__ __device__ constexpr uint32_t fwd_stages_for(uint32_t prefixes) { retur
 constexpr uint32_t fwd_slots = 8;
 constexpr uint32_t fwd_slot_columns = 64;
 constexpr uint32_t fwd_tmem_columns = 512;
-constexpr uint32_t fwd_epilogue_warps = 16;
+#ifndef SC_FWD_EPILOGUE_WARPS
+#define SC_FWD_EPILOGUE_WARPS 16
+#endif
+constexpr uint32_t fwd_epilogue_warps = SC_FWD_EPILOGUE_WARPS; // 16: four per scheduler at 96 registers; 8: two at 168
 constexpr uint32_t fwd_epilogue_threads = fwd_epilogue_warps * 32;
-constexpr uint32_t fwd_chunk_columns = 16; // columns of a tile that one epilogue warp owns
-constexpr uint32_t fwd_producer_warp = 16;
-constexpr uint32_t fwd_mma_warp = 17;
-constexpr uint32_t fwd_first_pull_warp = 18;
+constexpr uint32_t fwd_chunk_columns = 16;                                  // columns handled per tensor-memory load
+constexpr uint32_t fwd_column_groups = fwd_epilogue_warps / 4;             // warps that share a lane quadrant
+constexpr uint32_t fwd_warp_columns = fwd_cols / fwd_column_groups;        // columns of a tile that one warp owns
+constexpr uint32_t fwd_warp_chunks = fwd_warp_columns / fwd_chunk_columns;
+constexpr uint32_t fwd_producer_warp = fwd_epilogue_warps;
+constexpr uint32_t fwd_mma_warp = fwd_epilogue_warps + 1;
+constexpr uint32_t fwd_first_pull_warp = fwd_epilogue_warps + 2;
 constexpr uint32_t fwd_pull_warps = 1;
 constexpr uint32_t fwd_threads = 32 * (fwd_epilogue_warps + 2 + fwd_pull_warps);
 constexpr uint32_t fwd_q_bytes = fwd_rows * fwd_depth * 2;
@@ -68,7 +74,7 @@ struct fwd_tail {
 };
 constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
 // Per epilogue warp: [2 buffers][prefixes][16 columns] candidate inverse norms, then [2][8] tile maxima.
-constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_chunk_columns + 8);
+constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_warp_columns + 8);
 constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
 // Per epilogue thread: inverse norm, loss and coefficient of every prefix, laid out [3 * prefixes][thread].
 __host__ __device__ constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
@@ -278,8 +284,8 @@ struct tile_cursor {
     }
 };
 
-// Sixteen epilogue warps: warp w owns tensor-memory lanes 32*(w%4).. (a quarter of the tile's rows) and the 16 columns
-// w/4 of the tile. The loop over prefixes is rolled (small code, few registers, four warps per scheduler): a prefix's
+// Epilogue warps: warp w owns tensor-memory lanes 32*(w%4).. (a quarter of the tile's rows) and the column group w/4 of
+// the tile (16 columns each with sixteen warps). The loop over prefixes is rolled (small code, few registers, four warps per scheduler): a prefix's
 // segment dots come out of tensor memory, its raw-dot gradients go back into the same slot, and a second rolled pass
 // reads them widest first to form the suffix sums. Per-thread sums that are indexed by prefix live in shared memory.
 template <int prefixes_>
@@ -287,18 +293,20 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                                               uint32_t store_base, float* norm_staging, float* thread_state,
                                               uint32_t tmem_base, wait_context const& ctx, uint32_t warp, uint32_t lane) {
     constexpr int columns = fwd_chunk_columns;
-    constexpr int norm_count = prefixes_ * columns;
+    constexpr int chunks = fwd_warp_chunks;
+    constexpr int warp_columns = fwd_warp_columns;
+    constexpr int norm_count = prefixes_ * warp_columns;
     constexpr int ahead_count = (norm_count + 31) / 32;
-    uint32_t const quadrant = warp % 4, quarter = warp / 4;
+    uint32_t const quadrant = warp % 4, group = warp / 4;
     uint32_t const row_local = quadrant * 32 + lane;
-    uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16) + quarter * columns;
+    uint32_t const lane_base = tmem_base + ((quadrant * 32u) << 16) + group * warp_columns;
     uint32_t const column_tiles = p.rows_c / fwd_cols;
     uint32_t const quantities = 2 + 2 * prefixes_;
     float const beta = p.scalars != nullptr ? __ldg(p.scalars) : p.beta;
     float const bias = p.scalars != nullptr ? __ldg(p.scalars + 1) : p.bias;
     row_constants const constants{beta, bias, p.weight, beta};
-    float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][8][16]
-    float* const staged_max = staged_norms + 2 * 8 * columns;                   // [2][8]
+    float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][8][warp_columns]
+    float* const staged_max = staged_norms + 2 * 8 * warp_columns;              // [2][8]
     float* const mine = thread_state + threadIdx.x;                             // [3 * prefixes_] strided by the thread count
     uint32_t tile_local = 0, buffer = 0, store_buffer = 0;
 
@@ -311,10 +319,10 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         uint32_t const column_tile = where.column_tile(p);
 #pragma unroll
         for (int j = 0; j < ahead_count; ++j) {
-            uint32_t const index = lane + 32 * j; // (prefix, column) = (index / 16, index % 16)
+            uint32_t const index = lane + 32 * j; // (prefix, column) = (index / warp_columns, index % warp_columns)
             if (index < norm_count)
-                ahead[j] = __ldg(p.c_inv + static_cast<size_t>(index / columns) * p.rows_c + column_tile * fwd_cols +
-                                 quarter * columns + index % columns);
+                ahead[j] = __ldg(p.c_inv + static_cast<size_t>(index / warp_columns) * p.rows_c + column_tile * fwd_cols +
+                                 group * warp_columns + index % warp_columns);
         }
         if (lane < prefixes_) ahead_max = __ldg(p.c_tile_max + static_cast<size_t>(lane) * column_tiles + column_tile);
     };
@@ -322,7 +330,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
         for (int j = 0; j < ahead_count; ++j) {
             uint32_t const index = lane + 32 * j;
-            if (index < norm_count) staged_norms[into * 8 * columns + index] = ahead[j];
+            if (index < norm_count) staged_norms[into * 8 * warp_columns + index] = ahead[j];
         }
         if (lane < prefixes_) staged_max[into * 8 + lane] = ahead_max;
         __syncwarp();
@@ -352,8 +360,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             g = 0.0f, ga = 0.0f;
         }
         uint32_t const column_tile = cursor.column_tile(p);
-        uint32_t const column = column_tile * fwd_cols + quarter * columns;
-        float const* const norms_now = staged_norms + buffer * 8 * columns;
+        uint32_t const column = column_tile * fwd_cols + group * warp_columns;
+        float const* const norms_now = staged_norms + buffer * 8 * warp_columns;
         // Is this a tile where every cell is a plain negative off the cosine floor?
         uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
         uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
@@ -370,18 +378,21 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         if (threadIdx.x == 0) trace_phase(p, 6, epilogue_clock);
 
         uint32_t const first_unit = tile_local * prefixes_;
-        uint64_t prefix[columns / 2];
+        uint64_t prefix[chunks][columns / 2];
 #pragma unroll
-        for (int c = 0; c < columns / 2; ++c) prefix[c] = 0ull;
+        for (int h = 0; h < chunks; ++h)
+#pragma unroll
+            for (int c = 0; c < columns / 2; ++c) prefix[h][c] = 0ull;
         uint64_t const bias2 = pack2(bias, bias);
 #pragma unroll 1
         for (int k = 0; k < prefixes_; ++k) {
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
-            uint32_t d[columns];
-            tmem_load_16(address, d);
+            uint32_t d[chunks][columns];
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
             // Candidate norms are read from the warp's staging buffer pair by pair, right where they are used (broadcast
-            // shared loads), which keeps sixteen registers free for interleaving the cells.
-            uint64_t const* const inv_c = reinterpret_cast<uint64_t const*>(norms_now + k * columns);
+            // shared loads), which keeps registers free for interleaving the cells.
+            uint64_t const* const inv_c = reinterpret_cast<uint64_t const*>(norms_now + k * warp_columns);
             float const inv_q = mine[k * fwd_epilogue_threads];
             float const row_beta = beta * inv_q;
             float loss = 0.0f, coefficient = 0.0f;
@@ -390,12 +401,16 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 uint64_t const row_beta2 = pack2(row_beta, row_beta);
                 uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull;
 #pragma unroll
-                for (int c = 0; c < columns / 2; ++c) {
-                    prefix[c] = add2(prefix[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
-                    uint64_t const raw = cell_fast2(prefix[c], inv_c[c], row_beta2, bias2, loss2, g2, coefficient2);
-                    float raw0, raw1;
-                    unpack2(raw, raw0, raw1);
-                    d[2 * c] = __float_as_uint(raw0), d[2 * c + 1] = __float_as_uint(raw1);
+                for (int h = 0; h < chunks; ++h) {
+#pragma unroll
+                    for (int c = 0; c < columns / 2; ++c) {
+                        prefix[h][c] = add2(prefix[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
+                        uint64_t const raw =
+                            cell_fast2(prefix[h][c], inv_c[h * (columns / 2) + c], row_beta2, bias2, loss2, g2, coefficient2);
+                        float raw0, raw1;
+                        unpack2(raw, raw0, raw1);
+                        d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
+                    }
                 }
                 float lo, hi, band_g;
                 unpack2(loss2, lo, hi);
@@ -408,70 +423,82 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 // sum of complement * (logit + bias) = sum of raw * dot + bias * sum of complement
                 ga += fmaf(bias, band_g, coefficient);
             } else {
-                // Which of this warp's 16 columns, if any, is the row's own copy or its pair partner.
+                // Which of this warp's columns, if any, is the row's own copy or its pair partner.
                 int64_t const first = static_cast<int64_t>(p.candidate_base + column);
                 int64_t const own_at = static_cast<int64_t>(global_row) - first;
                 int64_t const partner_at = static_cast<int64_t>(global_row ^ 1ull) - first;
-                int const own_column = own_at >= 0 && own_at < columns ? static_cast<int>(own_at) : -1;
+                int const own_column = own_at >= 0 && own_at < warp_columns ? static_cast<int>(own_at) : -1;
                 int const partner_column =
-                    (p.spec_code & 1u) != 0u && partner_at >= 0 && partner_at < columns ? static_cast<int>(partner_at) : -1;
+                    (p.spec_code & 1u) != 0u && partner_at >= 0 && partner_at < warp_columns ? static_cast<int>(partner_at) : -1;
 #pragma unroll
-                for (int c = 0; c < columns / 2; ++c) {
-                    prefix[c] = add2(prefix[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
-                    float dot0, dot1, norm0, norm1;
-                    unpack2(prefix[c], dot0, dot1);
-                    unpack2(inv_c[c], norm0, norm1);
-                    d[2 * c] = __float_as_uint(cell_general(dot0, inv_q, norm0, constants, 2 * c == own_column,
-                                                            2 * c == partner_column, p.spec_code, loss, g, ga, coefficient));
-                    d[2 * c + 1] = __float_as_uint(cell_general(dot1, inv_q, norm1, constants, 2 * c + 1 == own_column,
-                                                                2 * c + 1 == partner_column, p.spec_code, loss, g, ga, coefficient));
+                for (int h = 0; h < chunks; ++h) {
+#pragma unroll
+                    for (int c = 0; c < columns / 2; ++c) {
+                        prefix[h][c] = add2(prefix[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
+                        float dot0, dot1, norm0, norm1;
+                        unpack2(prefix[h][c], dot0, dot1);
+                        unpack2(inv_c[h * (columns / 2) + c], norm0, norm1);
+                        int const at = h * columns + 2 * c;
+                        d[h][2 * c] = __float_as_uint(cell_general(dot0, inv_q, norm0, constants, at == own_column,
+                                                                   at == partner_column, p.spec_code, loss, g, ga, coefficient));
+                        d[h][2 * c + 1] = __float_as_uint(cell_general(dot1, inv_q, norm1, constants, at + 1 == own_column,
+                                                                       at + 1 == partner_column, p.spec_code, loss, g, ga,
+                                                                       coefficient));
+                    }
                 }
             }
-            tmem_store_16(address, d);
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) tmem_store_16(address + h * columns, d[h]);
             mine[(prefixes_ + k) * fwd_epilogue_threads] += loss;
             mine[(2 * prefixes_ + k) * fwd_epilogue_threads] += coefficient;
         }
         tmem_store_wait();
         if (threadIdx.x == 0) trace_phase(p, 7, epilogue_clock);
         // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
-        uint64_t running[columns / 2];
+        uint64_t running[chunks][columns / 2];
 #pragma unroll
-        for (int c = 0; c < columns / 2; ++c) running[c] = 0ull;
+        for (int h = 0; h < chunks; ++h)
+#pragma unroll
+            for (int c = 0; c < columns / 2; ++c) running[h][c] = 0ull;
 #pragma unroll 1
         for (int k = prefixes_ - 1; k >= 0; --k) {
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
-            uint32_t d[columns];
-            tmem_load_16(address, d);
-            tmem_load_wait();
-            uint32_t packed[columns / 2];
+            uint32_t d[chunks][columns];
 #pragma unroll
-            for (int c = 0; c < columns / 2; ++c) {
-                running[c] = add2(running[c], pack2(__uint_as_float(d[2 * c]), __uint_as_float(d[2 * c + 1])));
-                float lo, hi;
-                unpack2(running[c], lo, hi);
-                packed[c] = pack_bf16x2(lo, hi);
+            for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
+            tmem_load_wait();
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) {
+                uint32_t packed[columns / 2];
+#pragma unroll
+                for (int c = 0; c < columns / 2; ++c) {
+                    running[h][c] = add2(running[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
+                    float lo, hi;
+                    unpack2(running[h][c], lo, hi);
+                    packed[c] = pack_bf16x2(lo, hi);
+                }
+                // A [32 rows x 16 columns] patch of the band goes to one of the warp's two staging buffers (32 bytes per
+                // row) and leaves as a TMA store issued by lane 0, so no load/store-unit instruction touches global memory
+                // and no other warp is waited for. Before a buffer is rewritten, the store that read it two patches ago
+                // must have finished reading.
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+                uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]),
+                             "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u + 16u), "r"(packed[4]),
+                             "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                     reinterpret_cast<uint64_t>(cube_map)),
+                                 "r"(patch), "r"(column + h * columns), "r"(strip * fwd_rows + quadrant * 32u), "r"(k)
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                store_buffer ^= 1u;
             }
-            // The warp's [32 rows x 16 columns] patch of the band goes to the warp's own staging buffer (32 bytes per row)
-            // and leaves as a TMA store issued by lane 0, so no load/store-unit instruction touches global memory and no
-            // other warp is waited for. Two buffers alternate: before a buffer is rewritten, the store that read it two
-            // bands ago must have finished reading.
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            __syncwarp();
-            uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]), "r"(packed[1]),
-                         "r"(packed[2]), "r"(packed[3]) : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u + 16u), "r"(packed[4]),
-                         "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                                 reinterpret_cast<uint64_t>(cube_map)),
-                             "r"(patch), "r"(column), "r"(strip * fwd_rows + quadrant * 32u), "r"(k)
-                             : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-            store_buffer ^= 1u;
         }
         if (threadIdx.x == 0) trace_phase(p, 8, epilogue_clock);
         // This warp is done with the tile's slots.
@@ -483,8 +510,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         }
         if (more) park(buffer ^ 1u);
         if (cursor.t + 1 == p.tiles_per_run) {
-            // One partial record per (run, column quarter, row); the 1/N weight and the mirror cell's factor two go in here.
-            uint32_t const slot = run * 4 + quarter;
+            // One partial record per (run, column group, row); the 1/N weight and the mirror cell's factor two go in here.
+            uint32_t const slot = run * fwd_column_groups + group;
             float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
             record[0] = p.weight * g;
             record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
@@ -612,7 +639,9 @@ void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, CUtenso
 
 } // namespace
 
-uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run) { return 4 * (rows_c / fwd_cols) / tiles_per_run; }
+uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run) {
+    return fwd_column_groups * (rows_c / fwd_cols) / tiles_per_run;
+}
 uint32_t forward_quantities(uint32_t prefixes) { return 2 + 2 * prefixes; }
 
 uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors) {

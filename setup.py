@@ -16,6 +16,9 @@ SOURCES = [os.path.join(CSRC, name) for name in (
     "collectives.cu", "loss_small.cu", "loss_fwd.cu", "loss_bwd.cu", "no_alloc.cu",
 )]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr"]
+# Tuning knob of the forward kernel (16 or 8 epilogue warps); the default is the measured best.
+if os.environ.get("SC_FWD_EPILOGUE_WARPS"):
+    NVCC_FLAGS.append("-DSC_FWD_EPILOGUE_WARPS=" + os.environ["SC_FWD_EPILOGUE_WARPS"])
 
 setup(
     name="scalingcontrasts_b200",
