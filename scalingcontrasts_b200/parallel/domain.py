@@ -385,6 +385,11 @@ class DeviceDomain(Domain):
         view = native().tensor_from_pointer(self.status_address(), [8], "int32", self.device.index)
         return [int(v) & 0xFFFFFFFF for v in view.cpu().tolist()]
 
+    def status_view(self, channel: int = 0) -> torch.Tensor:
+        """The eight status words of a channel as a device tensor (for callers that copy them out with their results)."""
+        address = self.address(channel * int(native().CONTROL_BYTES) + int(native().STATUS_OFFSET))
+        return native().tensor_from_pointer(address, [8], "int32", self.device.index)
+
     def set_budget(self, seconds: float) -> None:
         self.budget_s = seconds
         for control in self._channels.values():

@@ -54,6 +54,12 @@ class ContrastiveTrainer:
         self._fed: Deque[Tuple[int, torch.cuda.Event]] = deque()
         self._next_slot = 0
         self._loss_host = torch.zeros(2, 16, dtype=torch.float32).pin_memory()
+        # Status words of the tile kernels and of the two collective channels travel to the host with every loss, so a
+        # wait that ran out (a peer that stopped) surfaces one step later without an extra synchronisation.
+        self._status_sources = [self.loss.engine.loss.status]
+        if hasattr(self.domain, "status_view"):
+            self._status_sources += [self.domain.status_view(0), self.domain.status_view(1)]
+        self._status_host = torch.zeros(2, len(self._status_sources), 8, dtype=torch.int32).pin_memory()
         self._loss_events = [torch.cuda.Event(), torch.cuda.Event()]
         self._loss_pending: Deque[int] = deque()
         for event in self._slot_free:
@@ -89,6 +95,8 @@ class ContrastiveTrainer:
         previous = self._collect_loss()
         index = self.steps_done % 2
         self._loss_host[index, :12].copy_(self.loss.last_summands, non_blocking=True)
+        for position, source in enumerate(self._status_sources):
+            self._status_host[index, position].copy_(source, non_blocking=True)
         self._loss_events[index].record()
         self._loss_pending.append(index)
         return previous
@@ -109,6 +117,11 @@ class ContrastiveTrainer:
             return None
         index = self._loss_pending.popleft()
         self._loss_events[index].synchronize()
+        codes = self._status_host[index, :, 0].tolist()
+        if any(codes):
+            names = ["loss kernels", "loss collectives", "gradient reducer"]
+            failed = ", ".join(f"{names[i]}: {self._status_host[index, i].tolist()}" for i, code in enumerate(codes) if code)
+            raise RuntimeError(f"a bounded device wait ran out during a training step ({failed})")
         return float(self._loss_host[index, 0])
 
     def last_loss(self) -> Optional[float]:
@@ -126,7 +139,7 @@ class ContrastiveTrainer:
         return self.rows * self.in_features * 2
 
     def d2h_bytes_per_step(self) -> int:
-        return 12 * 4
+        return 12 * 4 + len(self._status_sources) * 8 * 4
 
     # -- checkpoints ------------------------------------------------------------------------------------------
     def state_dict(self) -> Dict[str, object]:

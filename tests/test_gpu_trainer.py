@@ -39,3 +39,19 @@ def test_smoke_entry_point():
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+def test_a_recorded_timeout_surfaces_with_the_next_loss():
+    """The status words ride along with every loss; a wait that ran out is reported without any extra synchronisation.
+    The failure is made on the host: the word is written the way a tile kernel would record it."""
+    from scalingcontrasts_b200.trainer import ContrastiveTrainer
+
+    trainer = ContrastiveTrainer(rows=256, in_features=128, mid_features=256, hidden=256, prefixes=3, device="cuda", seed=1)
+    batch = torch.randn(256, 128).to(torch.bfloat16).pin_memory()
+    trainer.step(batch)
+    assert trainer.last_loss() is not None
+    trainer.loss.engine.loss.status[0] = 2
+    trainer.step(batch)
+    with pytest.raises(RuntimeError, match="bounded device wait"):
+        trainer.last_loss()
+    trainer.close()
