@@ -62,7 +62,7 @@ constexpr uint32_t fwd_c_bytes = fwd_cols * fwd_depth * 2;
 constexpr uint32_t fwd_stage_bytes = fwd_q_bytes + fwd_c_bytes;
 constexpr uint32_t fwd_tile_barriers = 8;
 constexpr float log2_e = 1.4426950408889634f;
-constexpr float small_decay_limit = 0.008f; // below this, log1p(e) = e - e^2/2 + e^3/3 to 1.3e-7 relative
+constexpr float small_decay_limit = 0.008f; // below this the cubic series of log1p(e) and e/(1+e) are exact to 5e-7
 
 struct fwd_tail {
     uint64_t stage_full[fwd_max_stages];
@@ -106,14 +106,33 @@ struct fwd_params {
     unsigned long long* trace; // optional: phase cycle counters of CTA 0 (see forward_trace_slots in api.h)
 };
 
-// Adds the cycles since `since` to a phase counter when tracing is on (CTA 0 only), and restarts the clock.
-__device__ __forceinline__ void trace_phase(fwd_params const& p, int slot, long long& since) {
-    if (p.trace != nullptr && blockIdx.x == 0) {
-        long long const now = clock64();
-        p.trace[slot] += static_cast<unsigned long long>(now - since);
-        since = now;
+// Phase timers: a role keeps its cycle counters in registers and adds them to the trace array once, when it is done, so
+// that timing a phase costs a clock read and not a round trip to memory. Only CTA 0 records.
+struct phase_timer {
+    long long since;
+    unsigned long long cycles[4];
+    bool on;
+    __device__ __forceinline__ explicit phase_timer(fwd_params const& p) : since(0), cycles{0, 0, 0, 0}, on(false) {
+#ifdef __CUDA_ARCH__
+        on = p.trace != nullptr && blockIdx.x == 0;
+        since = clock64();
+#endif
     }
-}
+    // Adds the cycles since the last call to counter `which` (0..3 of this role) and restarts the clock.
+    __device__ __forceinline__ void lap(int which) {
+#ifdef __CUDA_ARCH__
+        if (on) {
+            long long const now = clock64();
+            cycles[which] += static_cast<unsigned long long>(now - since);
+            since = now;
+        }
+#endif
+    }
+    __device__ __forceinline__ void flush(fwd_params const& p, int first_slot, int count) {
+        if (on)
+            for (int i = 0; i < count; ++i) p.trace[first_slot + i] += cycles[i];
+    }
+};
 
 // ---- the cell math ----------------------------------------------------------------------------------------------
 // Accumulators are kept without the 1/N weight: `g` sums -mask*z*(1-sigmoid(s)), `ga` sums that times (logit+bias),
@@ -121,33 +140,6 @@ __device__ __forceinline__ void trace_phase(fwd_params const& p, int slot, long 
 struct row_constants {
     float beta, bias, weight, raw_scale;
 };
-
-// A negative cell whose cosine is off the floor has z = -1 and s = -(logit + bias). The fast path handles two such cells
-// at once on packed pairs and returns their gradients with respect to the raw dot product WITHOUT the factor 2/N (mirror
-// cell and weight), which the backward kernel applies once per element. `loss`, `g` and `coefficient` are pairs of partial
-// sums whose halves are added when the band is done. The log1p(exp(-|a|)) part of the loss is left to the caller, which
-// gets the pair of decays exp(-|a|) in `decay` and their running sum in `decay_sum`.
-__device__ __forceinline__ uint64_t cell_fast2(uint64_t prefix_dot, uint64_t inv_c, uint64_t row_beta, uint64_t bias,
-                                               uint64_t& loss, uint64_t& g, uint64_t& coefficient, uint64_t& decay,
-                                               uint64_t& decay_sum) {
-    uint64_t const scale = mul2(inv_c, row_beta);
-    uint64_t const a = fma2(prefix_dot, scale, bias);
-    float a0, a1;
-    unpack2(a, a0, a1);
-    float const e0 = fast_ex2(-fabsf(a0) * log2_e), e1 = fast_ex2(-fabsf(a1) * log2_e);
-    uint64_t const e = pack2(e0, e1);
-    float s0, s1;
-    unpack2(add2(e, pack2(1.0f, 1.0f)), s0, s1);
-    uint64_t const r = pack2(fast_rcp(s0), fast_rcp(s1));
-    uint64_t const complement = mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), r);
-    loss = add2(loss, pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
-    decay = e;
-    decay_sum = add2(decay_sum, e);
-    g = add2(g, complement);
-    uint64_t const raw = mul2(complement, scale);
-    coefficient = fma2(raw, prefix_dot, coefficient);
-    return raw;
-}
 
 // Any cell: positives, the diagonal, floored cosines.
 __device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, float inv_c, row_constants const& k, bool own,
@@ -192,15 +184,15 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
                                               uint32_t const stages) {
     uint32_t stage = 0, phase = 0;
     uint32_t const chunks = p.hidden / fwd_depth;
-    long long clock = clock64();
+    phase_timer timer(p);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t const column_tile = run * p.tiles_per_run + t;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
-                trace_phase(p, 0, clock);
+                timer.lap(0);
                 if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
-                trace_phase(p, 1, clock);
+                timer.lap(1);
                 uint32_t const full = smem_u32(&tail->stage_full[stage]);
                 uint32_t const destination = stages_base + stage * fwd_stage_bytes;
                 mbar_arrive_expect_tx(full, fwd_stage_bytes);
@@ -211,6 +203,7 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
             }
         }
     }
+    timer.flush(p, 0, 2);
 }
 
 // The UMMA issuer is one thread, and a 128 x 64 x 16 UMMA occupies the tensor pipe for only ~32 cycles, so the loop
@@ -237,24 +230,24 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     }
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
     uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0;
-    long long clock = clock64();
+    phase_timer timer(p);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t slot_address = 0, accumulate = 0;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
                 uint32_t const starts = tail->band_starts[chunk];
-                trace_phase(p, 2, clock);
+                timer.lap(0);
                 if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
-                trace_phase(p, 3, clock);
+                timer.lap(1);
                 tcgen05_fence_after();
                 uint32_t const low = low_base + stage * (fwd_stage_bytes >> 4);
 #pragma unroll
                 for (int sub = 3; sub >= 0; --sub) {
                     if ((starts >> (8 * sub)) & 0xFFu) {
                         uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
-                        trace_phase(p, 2, clock);
+                        timer.lap(0);
                         if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
-                        trace_phase(p, 4, clock);
+                        timer.lap(2);
                         tcgen05_fence_after();
                         slot_address = tmem_base + slot * fwd_slot_columns;
                         accumulate = 0;
@@ -274,6 +267,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
             ++tile_local;
         }
     }
+    timer.flush(p, 2, 3);
 }
 
 // Position of a CTA in its fixed walk over (work item, tile of the run).
@@ -345,7 +339,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     float g = 0.0f, ga = 0.0f;
     uint32_t row = 0;
     uint64_t global_row = 0;
-    long long epilogue_clock = clock64();
+    phase_timer timer(p);
+    timer.on = timer.on && threadIdx.x == 0;
 
     while (cursor.valid(p)) {
         tile_cursor const following = cursor.next(p);
@@ -374,12 +369,12 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         for (int k = 0; k < prefixes_; ++k) special |= mine[k * fwd_epilogue_threads] * staged_max[buffer * 8 + k] >= 100.0f;
         special = __any_sync(0xFFFFFFFFu, special);
 
-        if (threadIdx.x == 0) trace_phase(p, 5, epilogue_clock);
+        timer.lap(0);
         if (!mbar_wait(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]), (tile_local / fwd_tile_barriers) & 1u, ctx,
                        site_fwd_tile_full, tile_local))
             return;
         tcgen05_fence_after();
-        if (threadIdx.x == 0) trace_phase(p, 6, epilogue_clock);
+        timer.lap(1);
 
         uint32_t const first_unit = tile_local * prefixes_;
         uint64_t prefix[chunks][columns / 2];
@@ -403,34 +398,48 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             tmem_load_wait();
             if (!special) {
                 uint64_t const row_beta2 = pack2(row_beta, row_beta);
-                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull, decay_sum = 0ull;
+                // First every cell's logit and decay e = exp(-|logit + bias|), with the sum of the decays and of the hinge
+                // terms max(logit + bias, 0). Where the warp's patch is all easy negatives (every decay tiny, every hinge
+                // zero, which is all but the hardest cells) the rest is a few packed multiply-adds: log1p(e) = e - e^2/2 +
+                // e^3/3 and 1 - sigmoid = e / (1 + e) = e - e^2 + e^3, both exact to better than 5e-7 below the limit.
+                // Otherwise the general form runs: reciprocal, select by sign, the full log1p polynomial.
                 uint64_t decay[chunks][columns / 2];
+                uint64_t decay_sum = 0ull, hinge = 0ull;
 #pragma unroll
                 for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                     for (int c = 0; c < columns / 2; ++c) {
                         prefix[h][c] = add2(prefix[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
-                        uint64_t const raw = cell_fast2(prefix[h][c], inv_c[h * (columns / 2) + c], row_beta2, bias2, loss2, g2,
-                                                        coefficient2, decay[h][c], decay_sum);
-                        float raw0, raw1;
-                        unpack2(raw, raw0, raw1);
-                        d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
+                        uint64_t const a = fma2(prefix[h][c], mul2(inv_c[h * (columns / 2) + c], row_beta2), bias2);
+                        float a0, a1;
+                        unpack2(a, a0, a1);
+                        decay[h][c] = pack2(fast_ex2(-fabsf(a0) * log2_e), fast_ex2(-fabsf(a1) * log2_e));
+                        decay_sum = add2(decay_sum, decay[h][c]);
+                        hinge = add2(hinge, pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
                     }
                 }
-                float lo, hi, band_g;
-                // log1p of the decays. Where every decay of the warp's patch is tiny (their sum stays under the limit, as
-                // it does for all but the hardest negatives), e - e^2/2 + e^3/3 is exact to 1.3e-7 and costs a third of
-                // the polynomial; otherwise the full polynomial runs.
+                float lo, hi, band_g, hinge_lo, hinge_hi;
                 unpack2(decay_sum, lo, hi);
-                if (__all_sync(0xFFFFFFFFu, lo + hi < small_decay_limit)) {
+                unpack2(hinge, hinge_lo, hinge_hi);
+                uint64_t loss2 = hinge, coefficient2 = 0ull, g2 = 0ull;
+                if (__all_sync(0xFFFFFFFFu, lo + hi < small_decay_limit && hinge_lo + hinge_hi == 0.0f)) {
                     uint64_t squares = 0ull, cubes = 0ull;
+                    uint64_t const minus_one = pack2(-1.0f, -1.0f);
 #pragma unroll
                     for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                         for (int c = 0; c < columns / 2; ++c) {
-                            uint64_t const square = mul2(decay[h][c], decay[h][c]);
+                            uint64_t const e = decay[h][c];
+                            uint64_t const square = mul2(e, e);
                             squares = add2(squares, square);
-                            cubes = fma2(square, decay[h][c], cubes);
+                            cubes = fma2(square, e, cubes);
+                            uint64_t const complement = fma2(square, add2(e, minus_one), e);
+                            g2 = add2(g2, complement);
+                            uint64_t const raw = mul2(complement, mul2(inv_c[h * (columns / 2) + c], row_beta2));
+                            coefficient2 = fma2(raw, prefix[h][c], coefficient2);
+                            float raw0, raw1;
+                            unpack2(raw, raw0, raw1);
+                            d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
                         }
                     }
                     loss2 = add2(loss2, decay_sum);
@@ -440,7 +449,23 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
                     for (int h = 0; h < chunks; ++h) {
 #pragma unroll
-                        for (int c = 0; c < columns / 2; ++c) loss2 = fma2(log1p_ratio2(decay[h][c]), decay[h][c], loss2);
+                        for (int c = 0; c < columns / 2; ++c) {
+                            uint64_t const e = decay[h][c];
+                            uint64_t const scale = mul2(inv_c[h * (columns / 2) + c], row_beta2);
+                            float a0, a1, e0, e1, s0, s1;
+                            unpack2(fma2(prefix[h][c], scale, bias2), a0, a1);
+                            unpack2(e, e0, e1);
+                            unpack2(add2(e, pack2(1.0f, 1.0f)), s0, s1);
+                            uint64_t const complement =
+                                mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), pack2(fast_rcp(s0), fast_rcp(s1)));
+                            loss2 = fma2(log1p_ratio2(e), e, loss2);
+                            g2 = add2(g2, complement);
+                            uint64_t const raw = mul2(complement, scale);
+                            coefficient2 = fma2(raw, prefix[h][c], coefficient2);
+                            float raw0, raw1;
+                            unpack2(raw, raw0, raw1);
+                            d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
+                        }
                     }
                 }
                 unpack2(loss2, lo, hi);
@@ -483,7 +508,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             mine[(2 * prefixes_ + k) * fwd_epilogue_threads] += coefficient;
         }
         tmem_store_wait();
-        if (threadIdx.x == 0) trace_phase(p, 7, epilogue_clock);
+        timer.lap(2);
         // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
         uint64_t running[chunks][columns / 2];
 #pragma unroll
@@ -530,7 +555,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 store_buffer ^= 1u;
             }
         }
-        if (threadIdx.x == 0) trace_phase(p, 8, epilogue_clock);
+        timer.lap(3);
         // This warp is done with the tile's slots.
         tcgen05_fence_before();
         __syncwarp();
@@ -556,6 +581,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         buffer ^= 1u;
         ++tile_local;
     }
+    timer.flush(p, 5, 4);
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
