@@ -62,7 +62,8 @@ constexpr uint32_t fwd_c_bytes = fwd_cols * fwd_depth * 2;
 constexpr uint32_t fwd_stage_bytes = fwd_q_bytes + fwd_c_bytes;
 constexpr uint32_t fwd_tile_barriers = 8;
 constexpr float log2_e = 1.4426950408889634f;
-constexpr float small_decay_limit = 0.008f; // below this the cubic series of log1p(e) and e/(1+e) are exact to 5e-7
+constexpr float easy_negative_limit = -8.0f; // (logit + bias) * log2(e) below this: e < 2^-8, the cubic series of log1p(e)
+                                             // and e / (1 + e) are then exact to 2e-8 relative
 
 struct fwd_tail {
     uint64_t stage_full[fwd_max_stages];
@@ -110,15 +111,15 @@ struct fwd_params {
 // that timing a phase costs a clock read and not a round trip to memory. Only CTA 0 records.
 struct phase_timer {
     long long since;
-    unsigned long long cycles[4];
+    unsigned long long cycles[8];
     bool on;
-    __device__ __forceinline__ explicit phase_timer(fwd_params const& p) : since(0), cycles{0, 0, 0, 0}, on(false) {
+    __device__ __forceinline__ explicit phase_timer(fwd_params const& p) : since(0), cycles{0, 0, 0, 0, 0, 0, 0, 0}, on(false) {
 #ifdef __CUDA_ARCH__
         on = p.trace != nullptr && blockIdx.x == 0;
         since = clock64();
 #endif
     }
-    // Adds the cycles since the last call to counter `which` (0..3 of this role) and restarts the clock.
+    // Adds the cycles since the last call to counter `which` (0..7 of this role) and restarts the clock.
     __device__ __forceinline__ void lap(int which) {
 #ifdef __CUDA_ARCH__
         if (on) {
@@ -141,10 +142,14 @@ struct row_constants {
     float beta, bias, weight, raw_scale;
 };
 
-// Any cell: positives, the diagonal, floored cosines.
-__device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, float inv_c, row_constants const& k, bool own,
-                                              bool partner, uint32_t spec_code, float& loss, float& g, float& ga,
-                                              float& coefficient) {
+// Any cell: positives, the diagonal, floored cosines. Only tiles that touch the diagonal or hold a floored norm come here,
+// so this is a real call (one copy of the code) rather than sixteen inlined ones: the kernel's hot loops stay small and
+// contiguous in the instruction cache. Returns what the cell adds to each of the row's sums.
+struct cell_outcome {
+    float raw, loss, cell, cell_logit, coefficient;
+};
+__device__ __noinline__ cell_outcome cell_general(float prefix_dot, float inv_q, float inv_c, float beta, float bias,
+                                                  float raw_scale, bool own, bool partner, uint32_t spec_code) {
     uint32_t const diagonal = (spec_code >> 1) & 3u; // 0 own, 1 negative, 2 skip
     float z = partner ? 1.0f : -1.0f;
     float mask = 1.0f;
@@ -155,18 +160,14 @@ __device__ __forceinline__ float cell_general(float prefix_dot, float inv_q, flo
     float const inverse_denominator = fminf(inv_q * inv_c, 100.0f);
     bool const floored = inverse_denominator >= 100.0f;
     float const cosine = floored ? 0.0f : prefix_dot * inverse_denominator;
-    float const logit = k.beta * (own ? 1.0f : cosine);
-    float const a = logit + k.bias;
+    float const logit = beta * (own ? 1.0f : cosine);
+    float const a = logit + bias;
     float const s = z * a;
     float const d = fast_ex2(-fabsf(s) * log2_e);
     float const complement = (s >= 0.0f ? d : 1.0f) * fast_rcp(1.0f + d);
     float const cell = -mask * z * complement;
-    loss += mask * (fmaxf(-s, 0.0f) + log1p_unit(d));
-    g += cell;
-    ga = fmaf(cell, a, ga);
-    float const raw = (own || floored) ? 0.0f : cell * inverse_denominator * k.raw_scale;
-    coefficient = fmaf(raw, prefix_dot, coefficient);
-    return raw;
+    float const raw = (own || floored) ? 0.0f : cell * inverse_denominator * raw_scale;
+    return cell_outcome{raw, mask * (fmaxf(-s, 0.0f) + log1p_unit(d)), cell, cell * a, raw * prefix_dot};
 }
 
 __device__ __forceinline__ void tmem_store_16(uint32_t taddr, uint32_t const (&r)[16]) {
@@ -398,32 +399,32 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             tmem_load_wait();
             if (!special) {
                 uint64_t const row_beta2 = pack2(row_beta, row_beta);
-                // First every cell's logit and decay e = exp(-|logit + bias|), with the sum of the decays and of the hinge
-                // terms max(logit + bias, 0). Where the warp's patch is all easy negatives (every decay tiny, every hinge
-                // zero, which is all but the hardest cells) the rest is a few packed multiply-adds: log1p(e) = e - e^2/2 +
-                // e^3/3 and 1 - sigmoid = e / (1 + e) = e - e^2 + e^3, both exact to better than 5e-7 below the limit.
-                // Otherwise the general form runs: reciprocal, select by sign, the full log1p polynomial.
+                // First every cell's decay e = exp(-|logit + bias|), computed in base two (the scale and the bias carry
+                // log2(e), so the exponential is one MUFU with operand modifiers), and the largest logit + bias of the
+                // thread's cells. Where the warp's patch is all easy negatives (every logit + bias below the limit, which
+                // is all but the hardest cells) the rest is a few packed multiply-adds: log1p(e) = e - e^2/2 + e^3/3 and
+                // 1 - sigmoid = e / (1 + e) = e - e^2 + e^3, both exact to better than 2e-8 relative below the limit.
+                // Otherwise the general form runs: reciprocal, select by sign, the full log1p polynomial, the hinge.
+                uint64_t const row_beta2_binary = pack2(row_beta * log2_e, row_beta * log2_e);
+                uint64_t const bias2_binary = pack2(bias * log2_e, bias * log2_e);
                 uint64_t decay[chunks][columns / 2];
-                uint64_t decay_sum = 0ull, hinge = 0ull;
+                float largest0 = -INFINITY, largest1 = -INFINITY;
 #pragma unroll
                 for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                     for (int c = 0; c < columns / 2; ++c) {
                         prefix[h][c] = add2(prefix[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
-                        uint64_t const a = fma2(prefix[h][c], mul2(inv_c[h * (columns / 2) + c], row_beta2), bias2);
+                        uint64_t const a = fma2(prefix[h][c], mul2(inv_c[h * (columns / 2) + c], row_beta2_binary), bias2_binary);
                         float a0, a1;
                         unpack2(a, a0, a1);
-                        decay[h][c] = pack2(fast_ex2(-fabsf(a0) * log2_e), fast_ex2(-fabsf(a1) * log2_e));
-                        decay_sum = add2(decay_sum, decay[h][c]);
-                        hinge = add2(hinge, pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
+                        decay[h][c] = pack2(fast_ex2(-fabsf(a0)), fast_ex2(-fabsf(a1)));
+                        largest0 = fmaxf(largest0, a0), largest1 = fmaxf(largest1, a1);
                     }
                 }
-                float lo, hi, band_g, hinge_lo, hinge_hi;
-                unpack2(decay_sum, lo, hi);
-                unpack2(hinge, hinge_lo, hinge_hi);
-                uint64_t loss2 = hinge, coefficient2 = 0ull, g2 = 0ull;
-                if (__all_sync(0xFFFFFFFFu, lo + hi < small_decay_limit && hinge_lo + hinge_hi == 0.0f)) {
-                    uint64_t squares = 0ull, cubes = 0ull;
+                float lo, hi, band_g;
+                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull;
+                if (__all_sync(0xFFFFFFFFu, fmaxf(largest0, largest1) < easy_negative_limit)) {
+                    uint64_t singles = 0ull, squares = 0ull, cubes = 0ull;
                     uint64_t const minus_one = pack2(-1.0f, -1.0f);
 #pragma unroll
                     for (int h = 0; h < chunks; ++h) {
@@ -431,6 +432,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                         for (int c = 0; c < columns / 2; ++c) {
                             uint64_t const e = decay[h][c];
                             uint64_t const square = mul2(e, e);
+                            singles = add2(singles, e);
                             squares = add2(squares, square);
                             cubes = fma2(square, e, cubes);
                             uint64_t const complement = fma2(square, add2(e, minus_one), e);
@@ -442,7 +444,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                             d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
                         }
                     }
-                    loss2 = add2(loss2, decay_sum);
+                    loss2 = singles;
                     loss2 = fma2(squares, pack2(-0.5f, -0.5f), loss2);
                     loss2 = fma2(cubes, pack2(1.0f / 3.0f, 1.0f / 3.0f), loss2);
                 } else {
@@ -458,7 +460,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                             unpack2(add2(e, pack2(1.0f, 1.0f)), s0, s1);
                             uint64_t const complement =
                                 mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), pack2(fast_rcp(s0), fast_rcp(s1)));
-                            loss2 = fma2(log1p_ratio2(e), e, loss2);
+                            loss2 = add2(fma2(log1p_ratio2(e), e, loss2), pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
                             g2 = add2(g2, complement);
                             uint64_t const raw = mul2(complement, scale);
                             coefficient2 = fma2(raw, prefix[h][c], coefficient2);
@@ -494,11 +496,17 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                         unpack2(prefix[h][c], dot0, dot1);
                         unpack2(inv_c[h * (columns / 2) + c], norm0, norm1);
                         int const at = h * columns + 2 * c;
-                        d[h][2 * c] = __float_as_uint(cell_general(dot0, inv_q, norm0, constants, at == own_column,
-                                                                   at == partner_column, p.spec_code, loss, g, ga, coefficient));
-                        d[h][2 * c + 1] = __float_as_uint(cell_general(dot1, inv_q, norm1, constants, at + 1 == own_column,
-                                                                       at + 1 == partner_column, p.spec_code, loss, g, ga,
-                                                                       coefficient));
+                        cell_outcome const first_cell = cell_general(dot0, inv_q, norm0, constants.beta, constants.bias,
+                                                                     constants.raw_scale, at == own_column, at == partner_column,
+                                                                     p.spec_code);
+                        cell_outcome const second_cell =
+                            cell_general(dot1, inv_q, norm1, constants.beta, constants.bias, constants.raw_scale,
+                                         at + 1 == own_column, at + 1 == partner_column, p.spec_code);
+                        d[h][2 * c] = __float_as_uint(first_cell.raw), d[h][2 * c + 1] = __float_as_uint(second_cell.raw);
+                        loss += first_cell.loss + second_cell.loss;
+                        g += first_cell.cell + second_cell.cell;
+                        ga += first_cell.cell_logit + second_cell.cell_logit;
+                        coefficient += first_cell.coefficient + second_cell.coefficient;
                     }
                 }
             }
@@ -522,6 +530,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
             for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
             tmem_load_wait();
+            timer.lap(3);
 #pragma unroll
             for (int h = 0; h < chunks; ++h) {
                 uint32_t packed[columns / 2];
@@ -538,6 +547,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 // must have finished reading.
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 __syncwarp();
+                timer.lap(4);
                 uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]),
                              "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
@@ -545,6 +555,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                              "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
                 fence_proxy_async();
                 __syncwarp();
+                timer.lap(5);
                 if (lane == 0) {
                     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                                      reinterpret_cast<uint64_t>(cube_map)),
@@ -553,9 +564,9 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 store_buffer ^= 1u;
+                timer.lap(6);
             }
         }
-        timer.lap(3);
         // This warp is done with the tile's slots.
         tcgen05_fence_before();
         __syncwarp();
@@ -580,8 +591,9 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         cursor = following;
         buffer ^= 1u;
         ++tile_local;
+        timer.lap(7);
     }
-    timer.flush(p, 5, 4);
+    timer.flush(p, 5, 8);
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
