@@ -103,25 +103,31 @@ struct wait_context {
 };
 
 // Waits for the phase with the given parity to complete. Returns false when the budget ran out or when another warp of
-// the CTA has already given up; in the first case the failure is recorded and the abort flag raised.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
-                                          uint32_t detail) {
-#pragma unroll 1
-    for (int spin = 0; spin < 256; ++spin)
-        if (mbar_try_wait(bar, parity)) return true;
+// the CTA has already given up; in the first case the failure is recorded and the abort flag raised. The common case (the
+// phase completes within a few attempts) is inlined; the timed part is one real call, so that a kernel with a dozen waits
+// carries its code once.
+static __device__ __noinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, uint32_t* status, uint64_t budget_ns,
+                                             uint32_t volatile* abort_flag, uint32_t site, uint32_t detail) {
     uint64_t const start = global_timer_ns();
 #pragma unroll 1
     for (;;) {
 #pragma unroll 1
         for (int spin = 0; spin < 64; ++spin)
             if (mbar_try_wait(bar, parity)) return true;
-        if (*ctx.abort_flag != 0u) return false;
-        if (global_timer_ns() - start > ctx.budget_ns) {
-            record_failure(ctx.status, status_timeout_pipeline, site, detail, parity, bar);
-            *ctx.abort_flag = 1u;
+        if (*abort_flag != 0u) return false;
+        if (global_timer_ns() - start > budget_ns) {
+            record_failure(status, status_timeout_pipeline, site, detail, parity, bar);
+            *abort_flag = 1u;
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
+                                          uint32_t detail) {
+#pragma unroll 1
+    for (int spin = 0; spin < 16; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_timed(bar, parity, ctx.status, ctx.budget_ns, ctx.abort_flag, site, detail);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -68,7 +68,7 @@ constexpr float easy_negative_limit = -8.0f; // (logit + bias) * log2(e) below t
 struct fwd_tail {
     uint64_t stage_full[fwd_max_stages];
     uint64_t stage_empty[fwd_max_stages];
-    uint64_t slot_empty[fwd_slots];
+    uint64_t tile_empty[fwd_slots]; // tile t's accumulators have been read by every epilogue warp (index t % fwd_slots)
     uint64_t tile_full[fwd_tile_barriers];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -111,15 +111,15 @@ struct fwd_params {
 // that timing a phase costs a clock read and not a round trip to memory. Only CTA 0 records.
 struct phase_timer {
     long long since;
-    unsigned long long cycles[8];
+    unsigned long long cycles[4];
     bool on;
-    __device__ __forceinline__ explicit phase_timer(fwd_params const& p) : since(0), cycles{0, 0, 0, 0, 0, 0, 0, 0}, on(false) {
+    __device__ __forceinline__ explicit phase_timer(fwd_params const& p) : since(0), cycles{0, 0, 0, 0}, on(false) {
 #ifdef __CUDA_ARCH__
         on = p.trace != nullptr && blockIdx.x == 0;
         since = clock64();
 #endif
     }
-    // Adds the cycles since the last call to counter `which` (0..7 of this role) and restarts the clock.
+    // Adds the cycles since the last call to counter `which` (0..3 of this role) and restarts the clock.
     __device__ __forceinline__ void lap(int which) {
 #ifdef __CUDA_ARCH__
         if (on) {
@@ -230,7 +230,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
         tail->band_starts[chunk] = word;
     }
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
-    uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0;
+    uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0, released = 0;
     phase_timer timer(p);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
@@ -245,10 +245,22 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
 #pragma unroll
                 for (int sub = 3; sub >= 0; --sub) {
                     if ((starts >> (8 * sub)) & 0xFFu) {
-                        uint32_t const slot = unit % fwd_slots, use = unit / fwd_slots;
-                        timer.lap(0);
-                        if (!mbar_wait(smem_u32(&tail->slot_empty[slot]), (use & 1u) ^ 1u, ctx, site_fwd_slot_empty, unit)) return;
-                        timer.lap(2);
+                        // The slot's last user was unit - fwd_slots; its tile must have been read out. Tiles are released
+                        // whole (one arrival per epilogue warp) and observed here strictly in order, so a barrier's parity
+                        // can never be a full turn ahead of the one waited for: tile X + fwd_slots cannot even be issued
+                        // before tile X's release has been seen.
+                        uint32_t const slot = unit % fwd_slots;
+                        if (unit >= fwd_slots) {
+                            uint32_t const needed = (unit - fwd_slots) / prefixes_;
+                            timer.lap(0);
+                            while (released <= needed) {
+                                if (!mbar_wait(smem_u32(&tail->tile_empty[released % fwd_slots]), (released / fwd_slots) & 1u, ctx,
+                                               site_fwd_slot_empty, unit))
+                                    return;
+                                ++released;
+                            }
+                            timer.lap(2);
+                        }
                         tcgen05_fence_after();
                         slot_address = tmem_base + slot * fwd_slot_columns;
                         accumulate = 0;
@@ -271,16 +283,18 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     timer.flush(p, 2, 3);
 }
 
-// Position of a CTA in its fixed walk over (work item, tile of the run).
+// Position of a CTA in its fixed walk over (work item, tile of the run). The item's strip and run are carried along, so
+// the division by the runtime run count happens once per item and not once per tile.
 struct tile_cursor {
-    uint32_t item, t;
+    uint32_t item, t, strip, run;
+    __device__ __forceinline__ static tile_cursor at(fwd_params const& p, uint32_t item) {
+        return tile_cursor{item, 0, item / p.runs_per_strip, item % p.runs_per_strip};
+    }
     __device__ __forceinline__ bool valid(fwd_params const& p) const { return item < p.items; }
     __device__ __forceinline__ tile_cursor next(fwd_params const& p) const {
-        return t + 1 < p.tiles_per_run ? tile_cursor{item, t + 1} : tile_cursor{item + gridDim.x, 0};
+        return t + 1 < p.tiles_per_run ? tile_cursor{item, t + 1, strip, run} : at(p, item + gridDim.x);
     }
-    __device__ __forceinline__ uint32_t column_tile(fwd_params const& p) const {
-        return (item % p.runs_per_strip) * p.tiles_per_run + t;
-    }
+    __device__ __forceinline__ uint32_t column_tile(fwd_params const& p) const { return run * p.tiles_per_run + t; }
 };
 
 // Epilogue warps: warp w owns tensor-memory lanes 32*(w%4).. (a quarter of the tile's rows) and the column group w/4 of
@@ -309,7 +323,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     float* const mine = thread_state + threadIdx.x;                             // [3 * prefixes_] strided by the thread count
     uint32_t tile_local = 0, buffer = 0, store_buffer = 0;
 
-    tile_cursor cursor{blockIdx.x, 0};
+    tile_cursor cursor = tile_cursor::at(p, blockIdx.x);
     if (!cursor.valid(p)) return;
     // Norms of a tile's candidates are fetched one tile ahead into registers and parked in this warp's shared-memory
     // buffer, so the cell loop reads them with broadcast shared loads instead of waiting on global memory.
@@ -347,7 +361,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         tile_cursor const following = cursor.next(p);
         bool const more = following.valid(p);
         if (more) fetch(following);
-        uint32_t const strip = cursor.item / p.runs_per_strip, run = cursor.item % p.runs_per_strip;
+        uint32_t const strip = cursor.strip, run = cursor.run;
         if (cursor.t == 0) {
             row = strip * fwd_rows + row_local;
             global_row = p.query_base + row;
@@ -530,7 +544,6 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
             for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
             tmem_load_wait();
-            timer.lap(3);
 #pragma unroll
             for (int h = 0; h < chunks; ++h) {
                 uint32_t packed[columns / 2];
@@ -547,7 +560,6 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 // must have finished reading.
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 __syncwarp();
-                timer.lap(4);
                 uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]),
                              "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
@@ -555,7 +567,6 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                              "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
                 fence_proxy_async();
                 __syncwarp();
-                timer.lap(5);
                 if (lane == 0) {
                     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                                      reinterpret_cast<uint64_t>(cube_map)),
@@ -564,16 +575,13 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 store_buffer ^= 1u;
-                timer.lap(6);
             }
         }
+        timer.lap(3);
         // This warp is done with the tile's slots.
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-            for (int k = 0; k < prefixes_; ++k) mbar_arrive(smem_u32(&tail->slot_empty[(first_unit + k) % fwd_slots]));
-        }
+        if (lane == 0) mbar_arrive(smem_u32(&tail->tile_empty[tile_local % fwd_slots]));
         if (more) park(buffer ^ 1u);
         if (cursor.t + 1 == p.tiles_per_run) {
             // One partial record per (run, column group, row); the 1/N weight and the mirror cell's factor two go in here.
@@ -591,9 +599,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         cursor = following;
         buffer ^= 1u;
         ++tile_local;
-        timer.lap(7);
     }
-    timer.flush(p, 5, 8);
+    timer.flush(p, 5, 4);
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
@@ -636,7 +643,7 @@ __global__ void __launch_bounds__(fwd_threads, 1)
             mbar_init(smem_u32(&tail->stage_full[i]), 1);
             mbar_init(smem_u32(&tail->stage_empty[i]), 1);
         }
-        for (uint32_t i = 0; i < fwd_slots; ++i) mbar_init(smem_u32(&tail->slot_empty[i]), fwd_epilogue_warps);
+        for (uint32_t i = 0; i < fwd_slots; ++i) mbar_init(smem_u32(&tail->tile_empty[i]), fwd_epilogue_warps);
         for (uint32_t i = 0; i < fwd_tile_barriers; ++i) mbar_init(smem_u32(&tail->tile_full[i]), 1);
         fence_barrier_init();
     }
