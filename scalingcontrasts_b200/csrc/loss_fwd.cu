@@ -72,7 +72,6 @@ struct fwd_tail {
     uint64_t tile_full[fwd_tile_barriers];
     uint32_t tmem_base;
     uint32_t abort_flag;
-    uint32_t band_starts[64]; // per 64-channel chunk, where bands begin (see mma_role); hidden <= 4096
 };
 constexpr uint32_t fwd_tail_bytes = (sizeof(fwd_tail) + 127) / 128 * 128;
 // Per epilogue warp: [2 buffers][prefixes][16 columns] candidate inverse norms, then [2][8] tile maxima.
@@ -80,10 +79,10 @@ constexpr uint32_t fwd_norm_floats_per_warp = 2 * (8 * fwd_warp_columns + 8);
 constexpr uint32_t fwd_norm_bytes = fwd_epilogue_warps * fwd_norm_floats_per_warp * 4;
 // Per epilogue thread: inverse norm, loss and coefficient of every prefix, laid out [3 * prefixes][thread].
 __host__ __device__ constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { return 3 * prefixes * fwd_epilogue_threads * 4; }
-// Per epilogue warp two staging buffers of [32 rows][16 columns] bfloat16, from which the warp's patch of a band's
-// gradient cube leaves through a TMA store while the next band is being computed.
+// Per epilogue warp two staging buffers (one per band of a pair) of [32 rows][16 columns] bfloat16 for each of the warp's
+// column chunks, from which the warp's patches of the gradient cube leave through TMA stores.
 constexpr uint32_t fwd_store_patch_bytes = 32 * fwd_chunk_columns * 2;
-constexpr uint32_t fwd_store_bytes = fwd_epilogue_warps * 2 * fwd_store_patch_bytes;
+constexpr uint32_t fwd_store_bytes = fwd_epilogue_warps * 2 * fwd_warp_chunks * fwd_store_patch_bytes;
 __host__ __device__ constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
     return 1024 + fwd_stages_for(prefixes) * fwd_stage_bytes + fwd_store_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
 }
@@ -105,6 +104,10 @@ struct fwd_params {
     uint64_t budget_ns;
     pull_request pull;
     unsigned long long* trace; // optional: phase cycle counters of CTA 0 (see forward_trace_slots in api.h)
+    // One word per 64-channel chunk, one byte per 16-channel step of the chunk: non-zero when, walking the channels
+    // downwards, the step is the first of a band (the topmost step, or the step just below a band's first channel).
+    // Kept in the kernel's parameters so that the UMMA warp reads it through the uniform datapath. hidden <= 4096.
+    uint32_t band_starts[64];
 };
 
 // Phase timers: a role keeps its cycle counters in registers and adds them to the trace array once, when it is done, so
@@ -180,26 +183,50 @@ __device__ __forceinline__ void tmem_store_16(uint32_t taddr, uint32_t const (&r
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- roles ------------------------------------------------------------------------------------------------------
+// The producer and UMMA roles are run by all 32 lanes of their warp, with only the TMA / UMMA / commit instructions
+// themselves under the elected lane's predicate: loop counters, stage addresses and descriptors are then warp-uniform
+// values the compiler can keep in uniform registers, which is where those instructions take their operands from. (Run
+// by a single lane inside a divergent branch, every operand would cross from a vector to a uniform register first.)
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(elected));
+    return elected != 0u;
+}
+// Every lane waits; the answer is the same in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
+                                               uint32_t detail) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, ctx, site, detail));
+}
+
 __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensorMap const* c_map, fwd_params const& p,
                                               uint32_t stages_base, fwd_tail* tail, wait_context const& ctx,
                                               uint32_t const stages) {
+    bool const elected = elect_one();
     uint32_t stage = 0, phase = 0;
     uint32_t const chunks = p.hidden / fwd_depth;
     phase_timer timer(p);
+    timer.on = timer.on && elected;
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t const column_tile = run * p.tiles_per_run + t;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
                 timer.lap(0);
-                if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
                 timer.lap(1);
                 uint32_t const full = smem_u32(&tail->stage_full[stage]);
                 uint32_t const destination = stages_base + stage * fwd_stage_bytes;
-                mbar_arrive_expect_tx(full, fwd_stage_bytes);
-                tma_load_2d(destination, q_map, full, chunk * static_cast<int>(fwd_depth), static_cast<int>(strip * fwd_rows));
-                tma_load_2d(destination + fwd_q_bytes, c_map, full, chunk * static_cast<int>(fwd_depth),
-                            static_cast<int>(column_tile * fwd_cols));
+                if (elected) {
+                    mbar_arrive_expect_tx(full, fwd_stage_bytes);
+                    tma_load_2d(destination, q_map, full, chunk * static_cast<int>(fwd_depth), static_cast<int>(strip * fwd_rows));
+                    tma_load_2d(destination + fwd_q_bytes, c_map, full, chunk * static_cast<int>(fwd_depth),
+                                static_cast<int>(column_tile * fwd_cols));
+                }
+                __syncwarp();
                 if (++stage == stages) stage = 0, phase ^= 1u;
             }
         }
@@ -207,38 +234,24 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
     timer.flush(p, 0, 2);
 }
 
-// The UMMA issuer is one thread, and a 128 x 64 x 16 UMMA occupies the tensor pipe for only ~32 cycles, so the loop
-// around each issue has to be a handful of instructions: descriptors are a constant high word plus a low word that
-// advances by fixed amounts, and where a band begins (walking the channels downwards) is read from a per-chunk flag
-// word prepared once in shared memory instead of being searched in the ladder.
 template <int prefixes_>
 __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_base, fwd_tail* tail, uint32_t tmem_base,
                                          wait_context const& ctx) {
     constexpr uint32_t idesc = umma_idesc_bf16(fwd_rows, fwd_cols);
     constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
+    bool const elected = elect_one();
     uint32_t const chunks = p.hidden / fwd_depth;
-    // band_starts[chunk] holds one byte per 16-channel step of the chunk: non-zero when, walking downwards, the step is
-    // the first of a band (the topmost step, or the step just below a band's first channel).
-    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
-        uint32_t word = 0;
-        for (uint32_t sub = 0; sub < 4; ++sub) {
-            uint32_t const above = (chunk * 4 + sub + 1) * 16; // first channel above this step
-            bool starts = above == p.hidden;
-            for (uint32_t band = 0; band + 1 < p.ladder.count; ++band) starts |= p.ladder.ends[band] == above;
-            word |= (starts ? 1u : 0u) << (8 * sub);
-        }
-        tail->band_starts[chunk] = word;
-    }
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
     uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0, released = 0;
     phase_timer timer(p);
+    timer.on = timer.on && elected;
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t slot_address = 0, accumulate = 0;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
-                uint32_t const starts = tail->band_starts[chunk];
+                uint32_t const starts = p.band_starts[chunk];
                 timer.lap(0);
-                if (!mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
                 timer.lap(1);
                 tcgen05_fence_after();
                 uint32_t const low = low_base + stage * (fwd_stage_bytes >> 4);
@@ -254,8 +267,8 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
                             uint32_t const needed = (unit - fwd_slots) / prefixes_;
                             timer.lap(0);
                             while (released <= needed) {
-                                if (!mbar_wait(smem_u32(&tail->tile_empty[released % fwd_slots]), (released / fwd_slots) & 1u, ctx,
-                                               site_fwd_slot_empty, unit))
+                                if (!mbar_wait_warp(smem_u32(&tail->tile_empty[released % fwd_slots]), (released / fwd_slots) & 1u,
+                                                    ctx, site_fwd_slot_empty, unit))
                                     return;
                                 ++released;
                             }
@@ -270,13 +283,15 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
                     uint64_t q_descriptor, c_descriptor;
                     asm("mov.b64 %0, {%1, %2};" : "=l"(q_descriptor) : "r"(q_low), "r"(descriptor_high));
                     asm("mov.b64 %0, {%1, %2};" : "=l"(c_descriptor) : "r"(q_low + (fwd_q_bytes >> 4)), "r"(descriptor_high));
-                    umma_bf16(slot_address, q_descriptor, c_descriptor, idesc, accumulate);
+                    if (elected) umma_bf16(slot_address, q_descriptor, c_descriptor, idesc, accumulate);
                     accumulate = 1;
                 }
-                umma_commit(smem_u32(&tail->stage_empty[stage]));
+                if (elected) umma_commit(smem_u32(&tail->stage_empty[stage]));
+                __syncwarp();
                 if (++stage == fwd_stages_for(prefixes_)) stage = 0, phase ^= 1u;
             }
-            umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
+            if (elected) umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
+            __syncwarp();
             ++tile_local;
         }
     }
@@ -321,7 +336,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     float* const staged_norms = norm_staging + warp * fwd_norm_floats_per_warp; // [2][8][warp_columns]
     float* const staged_max = staged_norms + 2 * 8 * warp_columns;              // [2][8]
     float* const mine = thread_state + threadIdx.x;                             // [3 * prefixes_] strided by the thread count
-    uint32_t tile_local = 0, buffer = 0, store_buffer = 0;
+    uint32_t tile_local = 0, buffer = 0;
+    uint32_t const warp_store_base = store_base + warp * (2u * chunks) * fwd_store_patch_bytes;
 
     tile_cursor cursor = tile_cursor::at(p, blockIdx.x);
     if (!cursor.valid(p)) return;
@@ -537,44 +553,84 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         for (int h = 0; h < chunks; ++h)
 #pragma unroll
             for (int c = 0; c < columns / 2; ++c) running[h][c] = 0ull;
-#pragma unroll 1
-        for (int k = prefixes_ - 1; k >= 0; --k) {
-            uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
-            uint32_t d[chunks][columns];
+        // Bands are taken two at a time: both loads are in flight together, both patches are staged behind one proxy
+        // fence, and both leave in one bulk group, so a tile pays the load -> convert -> stage -> fence -> store latency
+        // chain three times for five bands instead of five times. A [32 rows x 16 columns] patch of a band goes to one of
+        // the warp's staging buffers (32 bytes per row) and leaves as a TMA store issued by lane 0, so no load/store-unit
+        // instruction touches global memory and no other warp is waited for. Before the buffers are rewritten, the
+        // stores that read them (the previous group) must have finished reading.
+        auto band_address = [&](int band) {
+            return lane_base + ((first_unit + (prefixes_ - 1 - band)) % fwd_slots) * fwd_slot_columns;
+        };
+        auto fold_and_pack = [&](uint32_t const (&d)[chunks][columns], uint32_t (&packed)[chunks][columns / 2]) {
 #pragma unroll
-            for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
-            tmem_load_wait();
-#pragma unroll
-            for (int h = 0; h < chunks; ++h) {
-                uint32_t packed[columns / 2];
+            for (int h = 0; h < chunks; ++h)
 #pragma unroll
                 for (int c = 0; c < columns / 2; ++c) {
                     running[h][c] = add2(running[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
                     float lo, hi;
                     unpack2(running[h][c], lo, hi);
-                    packed[c] = pack_bf16x2(lo, hi);
+                    packed[h][c] = pack_bf16x2(lo, hi);
                 }
-                // A [32 rows x 16 columns] patch of the band goes to one of the warp's two staging buffers (32 bytes per
-                // row) and leaves as a TMA store issued by lane 0, so no load/store-unit instruction touches global memory
-                // and no other warp is waited for. Before a buffer is rewritten, the store that read it two patches ago
-                // must have finished reading.
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                __syncwarp();
-                uint32_t const patch = store_base + (warp * 2u + store_buffer) * fwd_store_patch_bytes;
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u), "r"(packed[0]),
-                             "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 32u + 16u), "r"(packed[4]),
-                             "r"(packed[5]), "r"(packed[6]), "r"(packed[7]) : "memory");
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                                     reinterpret_cast<uint64_t>(cube_map)),
-                                 "r"(patch), "r"(column + h * columns), "r"(strip * fwd_rows + quadrant * 32u), "r"(k)
-                                 : "memory");
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
-                store_buffer ^= 1u;
+        };
+        auto stage_patches = [&](uint32_t const (&packed)[chunks][columns / 2], uint32_t half) {
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) {
+                uint32_t const patch = warp_store_base + (half * chunks + h) * fwd_store_patch_bytes + lane * 32u;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch), "r"(packed[h][0]), "r"(packed[h][1]),
+                             "r"(packed[h][2]), "r"(packed[h][3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(patch + 16u), "r"(packed[h][4]), "r"(packed[h][5]),
+                             "r"(packed[h][6]), "r"(packed[h][7]) : "memory");
+            }
+        };
+        auto send_patches = [&](uint32_t half, int band) {
+#pragma unroll
+            for (int h = 0; h < chunks; ++h)
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(cube_map)),
+                             "r"(warp_store_base + (half * chunks + h) * fwd_store_patch_bytes), "r"(column + h * columns),
+                             "r"(strip * fwd_rows + quadrant * 32u), "r"(band)
+                             : "memory");
+        };
+        int k = prefixes_ - 1;
+#pragma unroll 1
+        for (; k >= 1; k -= 2) {
+            uint32_t upper[chunks][columns], lower[chunks][columns];
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) tmem_load_16(band_address(k) + h * columns, upper[h]);
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) tmem_load_16(band_address(k - 1) + h * columns, lower[h]);
+            tmem_load_wait();
+            uint32_t packed_upper[chunks][columns / 2], packed_lower[chunks][columns / 2];
+            fold_and_pack(upper, packed_upper);
+            fold_and_pack(lower, packed_lower);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            stage_patches(packed_upper, 0);
+            stage_patches(packed_lower, 1);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                send_patches(0, k);
+                send_patches(1, k - 1);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+        if (k == 0) {
+            uint32_t last[chunks][columns];
+#pragma unroll
+            for (int h = 0; h < chunks; ++h) tmem_load_16(band_address(0) + h * columns, last[h]);
+            tmem_load_wait();
+            uint32_t packed_last[chunks][columns / 2];
+            fold_and_pack(last, packed_last);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            stage_patches(packed_last, 0);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                send_patches(0, 0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         }
         timer.lap(3);
@@ -668,9 +724,9 @@ __global__ void __launch_bounds__(fwd_threads, 1)
         epilogue_role<prefixes_>(&cube_map, p, tail, stages_base + fwd_stages_for(prefixes_) * fwd_stage_bytes, norm_staging,
                                  norm_staging + fwd_norm_bytes / 4, tmem_base, ctx, warp, lane);
     } else if (warp == fwd_producer_warp) {
-        if (lane == 0) producer_role(&q_map, &c_map, p, stages_base, tail, ctx, fwd_stages_for(prefixes_));
+        producer_role(&q_map, &c_map, p, stages_base, tail, ctx, fwd_stages_for(prefixes_));
     } else if (warp == fwd_mma_warp) {
-        if (lane == 0) mma_role<prefixes_>(p, stages_base, tail, tmem_base, ctx);
+        mma_role<prefixes_>(p, stages_base, tail, tmem_base, ctx);
     } else {
         pull_role(p.pull, threadIdx.x - fwd_first_pull_warp * 32);
     }
@@ -755,6 +811,16 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     p.budget_ns = a.budget_ns;
     p.pull = a.pull;
     p.trace = a.trace;
+    for (uint32_t chunk = 0; chunk < a.hidden / fwd_depth; ++chunk) {
+        uint32_t word = 0;
+        for (uint32_t sub = 0; sub < 4; ++sub) {
+            uint32_t const above = (chunk * 4 + sub + 1) * 16; // first channel above this step
+            bool starts = above == a.hidden;
+            for (uint32_t band = 0; band + 1 < a.ladder.count; ++band) starts |= a.ladder.ends[band] == above;
+            word |= (starts ? 1u : 0u) << (8 * sub);
+        }
+        p.band_starts[chunk] = word;
+    }
 
     CUtensorMap const q_map = make_map_2d(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
     CUtensorMap const c_map = make_map_2d(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
