@@ -68,7 +68,10 @@ constexpr float easy_negative_limit = -8.0f; // (logit + bias) * log2(e) below t
 struct fwd_tail {
     uint64_t stage_full[fwd_max_stages];
     uint64_t stage_empty[fwd_max_stages];
-    uint64_t tile_empty[fwd_slots]; // tile t's accumulators have been read by every epilogue warp (index t % fwd_slots)
+    // Tile t's accumulators have been read by every epilogue warp (index t % fwd_slots): `early` covers the two widest
+    // bands, which the suffix pass reads first and whose slots the next tile's UMMAs want first; `late` covers the rest.
+    uint64_t tile_early[fwd_slots];
+    uint64_t tile_late[fwd_slots];
     uint64_t tile_full[fwd_tile_barriers];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -242,7 +245,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     bool const elected = elect_one();
     uint32_t const chunks = p.hidden / fwd_depth;
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
-    uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0, released = 0;
+    uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0, seen_early = 0, seen_late = 0;
     phase_timer timer(p);
     timer.on = timer.on && elected;
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
@@ -258,19 +261,28 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
 #pragma unroll
                 for (int sub = 3; sub >= 0; --sub) {
                     if ((starts >> (8 * sub)) & 0xFFu) {
-                        // The slot's last user was unit - fwd_slots; its tile must have been read out. Tiles are released
-                        // whole (one arrival per epilogue warp) and observed here strictly in order, so a barrier's parity
-                        // can never be a full turn ahead of the one waited for: tile X + fwd_slots cannot even be issued
-                        // before tile X's release has been seen.
+                        // The slot's last user was unit - fwd_slots, band `rank` (counted from the widest) of tile `needed`;
+                        // the epilogue must have read it out. Releases are observed here strictly in tile order, per
+                        // barrier array, so a barrier's parity can never be a full turn ahead of the one waited for: tile
+                        // X + fwd_slots cannot even be issued before tile X's release has been seen.
                         uint32_t const slot = unit % fwd_slots;
                         if (unit >= fwd_slots) {
-                            uint32_t const needed = (unit - fwd_slots) / prefixes_;
+                            uint32_t const needed = (unit - fwd_slots) / prefixes_, rank = (unit - fwd_slots) % prefixes_;
                             timer.lap(0);
-                            while (released <= needed) {
-                                if (!mbar_wait_warp(smem_u32(&tail->tile_empty[released % fwd_slots]), (released / fwd_slots) & 1u,
-                                                    ctx, site_fwd_slot_empty, unit))
-                                    return;
-                                ++released;
+                            if (rank < 2) {
+                                while (seen_early <= needed) {
+                                    if (!mbar_wait_warp(smem_u32(&tail->tile_early[seen_early % fwd_slots]),
+                                                        (seen_early / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit))
+                                        return;
+                                    ++seen_early;
+                                }
+                            } else {
+                                while (seen_late <= needed) {
+                                    if (!mbar_wait_warp(smem_u32(&tail->tile_late[seen_late % fwd_slots]),
+                                                        (seen_late / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit))
+                                        return;
+                                    ++seen_late;
+                                }
                             }
                             timer.lap(2);
                         }
@@ -592,6 +604,11 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                              "r"(strip * fwd_rows + quadrant * 32u), "r"(band)
                              : "memory");
         };
+        auto release = [&](uint64_t* barriers) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&barriers[tile_local % fwd_slots]));
+        };
         int k = prefixes_ - 1;
 #pragma unroll 1
         for (; k >= 1; k -= 2) {
@@ -601,6 +618,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
             for (int h = 0; h < chunks; ++h) tmem_load_16(band_address(k - 1) + h * columns, lower[h]);
             tmem_load_wait();
+            if (k == prefixes_ - 1) release(tail->tile_early);
             uint32_t packed_upper[chunks][columns / 2], packed_lower[chunks][columns / 2];
             fold_and_pack(upper, packed_upper);
             fold_and_pack(lower, packed_lower);
@@ -621,6 +639,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
             for (int h = 0; h < chunks; ++h) tmem_load_16(band_address(0) + h * columns, last[h]);
             tmem_load_wait();
+            if (prefixes_ == 1) release(tail->tile_early);
             uint32_t packed_last[chunks][columns / 2];
             fold_and_pack(last, packed_last);
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -635,9 +654,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         }
         timer.lap(3);
         // This warp is done with the tile's slots.
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&tail->tile_empty[tile_local % fwd_slots]));
+        release(tail->tile_late);
         if (more) park(buffer ^ 1u);
         if (cursor.t + 1 == p.tiles_per_run) {
             // One partial record per (run, column group, row); the 1/N weight and the mirror cell's factor two go in here.
@@ -699,7 +716,10 @@ __global__ void __launch_bounds__(fwd_threads, 1)
             mbar_init(smem_u32(&tail->stage_full[i]), 1);
             mbar_init(smem_u32(&tail->stage_empty[i]), 1);
         }
-        for (uint32_t i = 0; i < fwd_slots; ++i) mbar_init(smem_u32(&tail->tile_empty[i]), fwd_epilogue_warps);
+        for (uint32_t i = 0; i < fwd_slots; ++i) {
+            mbar_init(smem_u32(&tail->tile_early[i]), fwd_epilogue_warps);
+            mbar_init(smem_u32(&tail->tile_late[i]), fwd_epilogue_warps);
+        }
         for (uint32_t i = 0; i < fwd_tile_barriers; ++i) mbar_init(smem_u32(&tail->tile_full[i]), 1);
         fence_barrier_init();
     }
