@@ -148,6 +148,11 @@ struct row_constants {
     float beta, bias, weight, raw_scale;
 };
 
+// The cell pass leaves each band's raw-dot gradients in tensor memory without the factor beta / |q_k| that is common to
+// the row and the band; the suffix pass multiplies it in while it sums the bands. A row of zero norm has an infinite
+// inverse norm and only zero gradients (its cosines are floored), so the factor is capped to keep 0 * factor at 0.
+__device__ __forceinline__ float row_factor(float beta, float inv_q) { return beta * fminf(inv_q, 1e30f); }
+
 // Any cell: positives, the diagonal, floored cosines. Only tiles that touch the diagonal or hold a floored norm come here,
 // so this is a real call (one copy of the code) rather than sixteen inlined ones: the kernel's hot loops stay small and
 // contiguous in the instruction cache. Returns what the cell adds to each of the row's sums.
@@ -436,7 +441,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             // shared loads), which keeps registers free for interleaving the cells.
             uint64_t const* const inv_c = reinterpret_cast<uint64_t const*>(norms_now + k * warp_columns);
             float const inv_q = mine[k * fwd_epilogue_threads];
-            float const row_beta = beta * inv_q;
+            float const row_beta = row_factor(beta, inv_q);
             float loss = 0.0f, coefficient = 0.0f;
             tmem_load_wait();
             if (!special) {
@@ -478,17 +483,17 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                             squares = add2(squares, square);
                             cubes = fma2(square, e, cubes);
                             uint64_t const complement = fma2(square, add2(e, minus_one), e);
-                            g2 = add2(g2, complement);
-                            uint64_t const raw = mul2(complement, mul2(inv_c[h * (columns / 2) + c], row_beta2));
+                            uint64_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
                             coefficient2 = fma2(raw, prefix[h][c], coefficient2);
                             float raw0, raw1;
                             unpack2(raw, raw0, raw1);
                             d[h][2 * c] = __float_as_uint(raw0), d[h][2 * c + 1] = __float_as_uint(raw1);
                         }
                     }
-                    loss2 = singles;
-                    loss2 = fma2(squares, pack2(-0.5f, -0.5f), loss2);
+                    // Both sums are combinations of the power sums: loss e - e^2/2 + e^3/3, complement e - e^2 + e^3.
+                    loss2 = fma2(squares, pack2(-0.5f, -0.5f), singles);
                     loss2 = fma2(cubes, pack2(1.0f / 3.0f, 1.0f / 3.0f), loss2);
+                    g2 = add2(fma2(squares, minus_one, singles), cubes);
                 } else {
 #pragma unroll
                     for (int h = 0; h < chunks; ++h) {
@@ -504,7 +509,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                                 mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), pack2(fast_rcp(s0), fast_rcp(s1)));
                             loss2 = add2(fma2(log1p_ratio2(e), e, loss2), pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
                             g2 = add2(g2, complement);
-                            uint64_t const raw = mul2(complement, scale);
+                            uint64_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
                             coefficient2 = fma2(raw, prefix[h][c], coefficient2);
                             float raw0, raw1;
                             unpack2(raw, raw0, raw1);
@@ -515,7 +520,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 unpack2(loss2, lo, hi);
                 loss = lo + hi;
                 unpack2(coefficient2, lo, hi);
-                coefficient = lo + hi;
+                coefficient = row_beta * (lo + hi);
                 unpack2(g2, lo, hi);
                 band_g = lo + hi;
                 g += band_g;
@@ -529,6 +534,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 int const own_column = own_at >= 0 && own_at < warp_columns ? static_cast<int>(own_at) : -1;
                 int const partner_column =
                     (p.spec_code & 1u) != 0u && partner_at >= 0 && partner_at < warp_columns ? static_cast<int>(partner_at) : -1;
+                float const without_row_factor = row_beta != 0.0f ? __fdividef(1.0f, row_beta) : 0.0f;
 #pragma unroll
                 for (int h = 0; h < chunks; ++h) {
 #pragma unroll
@@ -544,7 +550,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                         cell_outcome const second_cell =
                             cell_general(dot1, inv_q, norm1, constants.beta, constants.bias, constants.raw_scale,
                                          at + 1 == own_column, at + 1 == partner_column, p.spec_code);
-                        d[h][2 * c] = __float_as_uint(first_cell.raw), d[h][2 * c + 1] = __float_as_uint(second_cell.raw);
+                        d[h][2 * c] = __float_as_uint(first_cell.raw * without_row_factor);
+                        d[h][2 * c + 1] = __float_as_uint(second_cell.raw * without_row_factor);
                         loss += first_cell.loss + second_cell.loss;
                         g += first_cell.cell + second_cell.cell;
                         ga += first_cell.cell_logit + second_cell.cell_logit;
@@ -574,12 +581,15 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         auto band_address = [&](int band) {
             return lane_base + ((first_unit + (prefixes_ - 1 - band)) % fwd_slots) * fwd_slot_columns;
         };
-        auto fold_and_pack = [&](uint32_t const (&d)[chunks][columns], uint32_t (&packed)[chunks][columns / 2]) {
+        auto fold_and_pack = [&](uint32_t const (&d)[chunks][columns], int band, uint32_t (&packed)[chunks][columns / 2]) {
+            float const factor = row_factor(beta, mine[band * fwd_epilogue_threads]);
+            uint64_t const factor2 = pack2(factor, factor);
 #pragma unroll
             for (int h = 0; h < chunks; ++h)
 #pragma unroll
                 for (int c = 0; c < columns / 2; ++c) {
-                    running[h][c] = add2(running[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
+                    running[h][c] =
+                        fma2(pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])), factor2, running[h][c]);
                     float lo, hi;
                     unpack2(running[h][c], lo, hi);
                     packed[h][c] = pack_bf16x2(lo, hi);
@@ -620,8 +630,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             tmem_load_wait();
             if (k == prefixes_ - 1) release(tail->tile_early);
             uint32_t packed_upper[chunks][columns / 2], packed_lower[chunks][columns / 2];
-            fold_and_pack(upper, packed_upper);
-            fold_and_pack(lower, packed_lower);
+            fold_and_pack(upper, k, packed_upper);
+            fold_and_pack(lower, k - 1, packed_lower);
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
             stage_patches(packed_upper, 0);
@@ -641,7 +651,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             tmem_load_wait();
             if (prefixes_ == 1) release(tail->tile_early);
             uint32_t packed_last[chunks][columns / 2];
-            fold_and_pack(last, packed_last);
+            fold_and_pack(last, 0, packed_last);
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             __syncwarp();
             stage_patches(packed_last, 0);
