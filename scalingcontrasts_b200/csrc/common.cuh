@@ -267,37 +267,24 @@ __device__ __forceinline__ float log1p_ratio(float x) {
 }
 
 // Packed pairs of float32 in one 64-bit register: sm_100 executes add / mul / fma on both halves in one instruction,
-// which halves the issue slots of the epilogue's arithmetic.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
+// which halves the issue slots of the epilogue's arithmetic. The compiler's own float2 intrinsics are used (not opaque
+// inline assembly), so it can keep the halves where the scalar instructions around them (MUFU, tensor-memory loads and
+// stores) want them and fold sign changes into operands.
+using pair_t = float2;
+__device__ __forceinline__ pair_t pack2(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ void unpack2(pair_t v, float& lo, float& hi) { lo = v.x, hi = v.y; }
+__device__ __forceinline__ pair_t add2(pair_t a, pair_t b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ pair_t mul2(pair_t a, pair_t b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ pair_t fma2(pair_t a, pair_t b, pair_t c) { return __ffma2_rn(a, b, c); }
 // log1p(x) / x for both halves of a pair (the same polynomial as log1p_ratio). The coefficients sit in constant memory
 // already duplicated into pairs, so that they can be operands of the packed instructions without register pairs of
 // their own.
 __constant__ float2 log1p_pairs[9] = {{SC_LOG1P_C0, SC_LOG1P_C0}, {SC_LOG1P_C1, SC_LOG1P_C1}, {SC_LOG1P_C2, SC_LOG1P_C2},
                                       {SC_LOG1P_C3, SC_LOG1P_C3}, {SC_LOG1P_C4, SC_LOG1P_C4}, {SC_LOG1P_C5, SC_LOG1P_C5},
                                       {SC_LOG1P_C6, SC_LOG1P_C6}, {SC_LOG1P_C7, SC_LOG1P_C7}, {SC_LOG1P_C8, SC_LOG1P_C8}};
-__device__ __forceinline__ uint64_t log1p_pair(int index) { return *reinterpret_cast<uint64_t const*>(&log1p_pairs[index]); }
-__device__ __forceinline__ uint64_t log1p_ratio2(uint64_t x) {
-    uint64_t p = log1p_pair(8);
+__device__ __forceinline__ pair_t log1p_pair(int index) { return log1p_pairs[index]; }
+__device__ __forceinline__ pair_t log1p_ratio2(pair_t x) {
+    pair_t p = log1p_pair(8);
     p = fma2(p, x, log1p_pair(7));
     p = fma2(p, x, log1p_pair(6));
     p = fma2(p, x, log1p_pair(5));

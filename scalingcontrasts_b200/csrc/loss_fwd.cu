@@ -425,12 +425,12 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         timer.lap(1);
 
         uint32_t const first_unit = tile_local * prefixes_;
-        uint64_t prefix[chunks][columns / 2];
+        pair_t prefix[chunks][columns / 2];
 #pragma unroll
         for (int h = 0; h < chunks; ++h)
 #pragma unroll
-            for (int c = 0; c < columns / 2; ++c) prefix[h][c] = 0ull;
-        uint64_t const bias2 = pack2(bias, bias);
+            for (int c = 0; c < columns / 2; ++c) prefix[h][c] = pack2(0.0f, 0.0f);
+        pair_t const bias2 = pack2(bias, bias);
 #pragma unroll 1
         for (int k = 0; k < prefixes_; ++k) {
             uint32_t const address = lane_base + ((first_unit + (prefixes_ - 1 - k)) % fwd_slots) * fwd_slot_columns;
@@ -439,51 +439,52 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             for (int h = 0; h < chunks; ++h) tmem_load_16(address + h * columns, d[h]);
             // Candidate norms are read from the warp's staging buffer pair by pair, right where they are used (broadcast
             // shared loads), which keeps registers free for interleaving the cells.
-            uint64_t const* const inv_c = reinterpret_cast<uint64_t const*>(norms_now + k * warp_columns);
+            pair_t const* const inv_c = reinterpret_cast<pair_t const*>(norms_now + k * warp_columns);
             float const inv_q = mine[k * fwd_epilogue_threads];
             float const row_beta = row_factor(beta, inv_q);
             float loss = 0.0f, coefficient = 0.0f;
             tmem_load_wait();
             if (!special) {
-                uint64_t const row_beta2 = pack2(row_beta, row_beta);
-                // First every cell's decay e = exp(-|logit + bias|), computed in base two (the scale and the bias carry
-                // log2(e), so the exponential is one MUFU with operand modifiers), and the largest logit + bias of the
-                // thread's cells. Where the warp's patch is all easy negatives (every logit + bias below the limit, which
-                // is all but the hardest cells) the rest is a few packed multiply-adds: log1p(e) = e - e^2/2 + e^3/3 and
-                // 1 - sigmoid = e / (1 + e) = e - e^2 + e^3, both exact to better than 2e-8 relative below the limit.
-                // Otherwise the general form runs: reciprocal, select by sign, the full log1p polynomial, the hinge.
-                uint64_t const row_beta2_binary = pack2(row_beta * log2_e, row_beta * log2_e);
-                uint64_t const bias2_binary = pack2(bias * log2_e, bias * log2_e);
-                uint64_t decay[chunks][columns / 2];
+                pair_t const row_beta2 = pack2(row_beta, row_beta);
+                // First every cell's e = exp(logit + bias), computed in base two (the scale and the bias carry log2(e), so
+                // the exponential is a single MUFU), and the largest logit + bias of the thread's cells. Where the warp's
+                // patch is all easy negatives (every logit + bias below the limit, which is all but the hardest cells) e
+                // is the decay exp(-|logit + bias|) and the rest is a few packed multiply-adds: log1p(e) = e - e^2/2 +
+                // e^3/3 and 1 - sigmoid = e / (1 + e) = e - e^2 + e^3, both exact to better than 2e-8 relative below the
+                // limit. Otherwise the general form runs: the decay with the absolute value, reciprocal, select by sign,
+                // the full log1p polynomial, the hinge.
+                pair_t const row_beta2_binary = pack2(row_beta * log2_e, row_beta * log2_e);
+                pair_t const bias2_binary = pack2(bias * log2_e, bias * log2_e);
+                pair_t decay[chunks][columns / 2];
                 float largest0 = -INFINITY, largest1 = -INFINITY;
 #pragma unroll
                 for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                     for (int c = 0; c < columns / 2; ++c) {
                         prefix[h][c] = add2(prefix[h][c], pack2(__uint_as_float(d[h][2 * c]), __uint_as_float(d[h][2 * c + 1])));
-                        uint64_t const a = fma2(prefix[h][c], mul2(inv_c[h * (columns / 2) + c], row_beta2_binary), bias2_binary);
+                        pair_t const a = fma2(prefix[h][c], mul2(inv_c[h * (columns / 2) + c], row_beta2_binary), bias2_binary);
                         float a0, a1;
                         unpack2(a, a0, a1);
-                        decay[h][c] = pack2(fast_ex2(-fabsf(a0)), fast_ex2(-fabsf(a1)));
+                        decay[h][c] = pack2(fast_ex2(a0), fast_ex2(a1));
                         largest0 = fmaxf(largest0, a0), largest1 = fmaxf(largest1, a1);
                     }
                 }
                 float lo, hi, band_g;
-                uint64_t loss2 = 0ull, coefficient2 = 0ull, g2 = 0ull;
+                pair_t loss2 = pack2(0.0f, 0.0f), coefficient2 = pack2(0.0f, 0.0f), g2 = pack2(0.0f, 0.0f);
                 if (__all_sync(0xFFFFFFFFu, fmaxf(largest0, largest1) < easy_negative_limit)) {
-                    uint64_t singles = 0ull, squares = 0ull, cubes = 0ull;
-                    uint64_t const minus_one = pack2(-1.0f, -1.0f);
+                    pair_t singles = pack2(0.0f, 0.0f), squares = pack2(0.0f, 0.0f), cubes = pack2(0.0f, 0.0f);
+                    pair_t const minus_one = pack2(-1.0f, -1.0f);
 #pragma unroll
                     for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                         for (int c = 0; c < columns / 2; ++c) {
-                            uint64_t const e = decay[h][c];
-                            uint64_t const square = mul2(e, e);
+                            pair_t const e = decay[h][c];
+                            pair_t const square = mul2(e, e);
                             singles = add2(singles, e);
                             squares = add2(squares, square);
                             cubes = fma2(square, e, cubes);
-                            uint64_t const complement = fma2(square, add2(e, minus_one), e);
-                            uint64_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
+                            pair_t const complement = fma2(square, add2(e, minus_one), e);
+                            pair_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
                             coefficient2 = fma2(raw, prefix[h][c], coefficient2);
                             float raw0, raw1;
                             unpack2(raw, raw0, raw1);
@@ -499,17 +500,17 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                     for (int h = 0; h < chunks; ++h) {
 #pragma unroll
                         for (int c = 0; c < columns / 2; ++c) {
-                            uint64_t const e = decay[h][c];
-                            uint64_t const scale = mul2(inv_c[h * (columns / 2) + c], row_beta2);
+                            pair_t const scale = mul2(inv_c[h * (columns / 2) + c], row_beta2);
                             float a0, a1, e0, e1, s0, s1;
                             unpack2(fma2(prefix[h][c], scale, bias2), a0, a1);
-                            unpack2(e, e0, e1);
+                            e0 = fast_ex2(-fabsf(a0) * log2_e), e1 = fast_ex2(-fabsf(a1) * log2_e);
+                            pair_t const e = pack2(e0, e1);
                             unpack2(add2(e, pack2(1.0f, 1.0f)), s0, s1);
-                            uint64_t const complement =
+                            pair_t const complement =
                                 mul2(pack2(a0 >= 0.0f ? 1.0f : e0, a1 >= 0.0f ? 1.0f : e1), pack2(fast_rcp(s0), fast_rcp(s1)));
                             loss2 = add2(fma2(log1p_ratio2(e), e, loss2), pack2(fmaxf(a0, 0.0f), fmaxf(a1, 0.0f)));
                             g2 = add2(g2, complement);
-                            uint64_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
+                            pair_t const raw = mul2(complement, inv_c[h * (columns / 2) + c]);
                             coefficient2 = fma2(raw, prefix[h][c], coefficient2);
                             float raw0, raw1;
                             unpack2(raw, raw0, raw1);
@@ -567,11 +568,11 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         tmem_store_wait();
         timer.lap(2);
         // Suffix sums, widest band first: band k's gradient cube holds the sum over bands >= k.
-        uint64_t running[chunks][columns / 2];
+        pair_t running[chunks][columns / 2];
 #pragma unroll
         for (int h = 0; h < chunks; ++h)
 #pragma unroll
-            for (int c = 0; c < columns / 2; ++c) running[h][c] = 0ull;
+            for (int c = 0; c < columns / 2; ++c) running[h][c] = pack2(0.0f, 0.0f);
         // Bands are taken two at a time: both loads are in flight together, both patches are staged behind one proxy
         // fence, and both leave in one bulk group, so a tile pays the load -> convert -> stage -> fence -> store latency
         // chain three times for five bands instead of five times. A [32 rows x 16 columns] patch of a band goes to one of
@@ -583,7 +584,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         };
         auto fold_and_pack = [&](uint32_t const (&d)[chunks][columns], int band, uint32_t (&packed)[chunks][columns / 2]) {
             float const factor = row_factor(beta, mine[band * fwd_epilogue_threads]);
-            uint64_t const factor2 = pack2(factor, factor);
+            pair_t const factor2 = pack2(factor, factor);
 #pragma unroll
             for (int h = 0; h < chunks; ++h)
 #pragma unroll
