@@ -107,7 +107,8 @@ struct forward_arguments {
     uint32_t spec_code;
     uint64_t budget_ns;
     pull_request pull;               // optional: bytes == 0 means nothing to pull
-    // Optional phase timers (device array of forward_trace_slots counters, zeroed by the caller): CTA 0 adds the cycles
+    // Optional phase timers, live only in a build with -DSC_FWD_TRACE=1 and ignored otherwise (device array of
+    // forward_trace_slots counters, zeroed by the caller): CTA 0 adds the cycles
     // it spends in 0 producer issue, 1 producer waiting for a free stage, 2 UMMA issue, 3 UMMA waiting for a stage,
     // 4 UMMA waiting for a slot, 5 epilogue between tiles, 6 epilogue waiting for a tile, 7 cell pass, 8 suffix pass.
     unsigned long long* trace;

@@ -113,8 +113,14 @@ struct fwd_params {
     uint32_t band_starts[64];
 };
 
-// Phase timers: a role keeps its cycle counters in registers and adds them to the trace array once, when it is done, so
-// that timing a phase costs a clock read and not a round trip to memory. Only CTA 0 records.
+// Phase timers, compiled in only with -DSC_FWD_TRACE=1 (a diagnostic build: the clock reads and their branches cost the
+// epilogue a few percent of its issue slots). A role keeps its cycle counters in registers and adds them to the trace
+// array once, when it is done, so that timing a phase costs a clock read and not a round trip to memory. Only CTA 0
+// records. Without the flag the type is empty and the `trace` argument is ignored.
+#ifndef SC_FWD_TRACE
+#define SC_FWD_TRACE 0
+#endif
+#if SC_FWD_TRACE
 struct phase_timer {
     long long since;
     unsigned long long cycles[4];
@@ -125,6 +131,7 @@ struct phase_timer {
         since = clock64();
 #endif
     }
+    __device__ __forceinline__ void only_if(bool keep) { on = on && keep; }
     // Adds the cycles since the last call to counter `which` (0..3 of this role) and restarts the clock.
     __device__ __forceinline__ void lap(int which) {
 #ifdef __CUDA_ARCH__
@@ -140,6 +147,14 @@ struct phase_timer {
             for (int i = 0; i < count; ++i) p.trace[first_slot + i] += cycles[i];
     }
 };
+#else
+struct phase_timer {
+    __device__ __forceinline__ explicit phase_timer(fwd_params const&) {}
+    __device__ __forceinline__ void only_if(bool) {}
+    __device__ __forceinline__ void lap(int) {}
+    __device__ __forceinline__ void flush(fwd_params const&, int, int) {}
+};
+#endif
 
 // ---- the cell math ----------------------------------------------------------------------------------------------
 // Accumulators are kept without the 1/N weight: `g` sums -mask*z*(1-sigmoid(s)), `ga` sums that times (logit+bias),
@@ -217,7 +232,7 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
     uint32_t stage = 0, phase = 0;
     uint32_t const chunks = p.hidden / fwd_depth;
     phase_timer timer(p);
-    timer.on = timer.on && elected;
+    timer.only_if(elected);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         uint32_t const strip = item / p.runs_per_strip, run = item % p.runs_per_strip;
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
@@ -252,7 +267,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
     uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
     uint32_t stage = 0, phase = 0, unit = 0, tile_local = 0, seen_early = 0, seen_late = 0;
     phase_timer timer(p);
-    timer.on = timer.on && elected;
+    timer.only_if(elected);
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
         for (uint32_t t = 0; t < p.tiles_per_run; ++t) {
             uint32_t slot_address = 0, accumulate = 0;
@@ -388,7 +403,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     uint32_t row = 0;
     uint64_t global_row = 0;
     phase_timer timer(p);
-    timer.on = timer.on && threadIdx.x == 0;
+    timer.only_if(threadIdx.x == 0);
 
     while (cursor.valid(p)) {
         tile_cursor const following = cursor.next(p);

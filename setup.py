@@ -19,6 +19,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,c
 # Tuning knob of the forward kernel (16 or 8 epilogue warps); the default is the measured best.
 if os.environ.get("SC_FWD_EPILOGUE_WARPS"):
     NVCC_FLAGS.append("-DSC_FWD_EPILOGUE_WARPS=" + os.environ["SC_FWD_EPILOGUE_WARPS"])
+# Diagnostic build of the forward kernel with in-kernel phase timers (the `trace` argument of `forward`).
+if os.environ.get("SC_FWD_TRACE"):
+    NVCC_FLAGS.append("-DSC_FWD_TRACE=" + os.environ["SC_FWD_TRACE"])
 
 setup(
     name="scalingcontrasts_b200",
