@@ -180,6 +180,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One lane of a converged warp, chosen by the hardware. Roles that issue TMA or UMMA instructions run warp-wide and put
+// only those instructions under this predicate, so that their operands stay warp-uniform values.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(elected));
+    return elected != 0u;
+}
 // Makes the mbarrier track the completion of every UMMA this thread issued before it.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -1,6 +1,6 @@
 // Backward tile kernel of the streamed loss: folds a block's per-band gradient cubes into the owner's rows,
 //   query_gradient[i, h] += sum_j G_band(h)[i, j] * candidate[j, h],
-// as tcgen05 GEMM tiles of 128 rows x up to 192 channels, the candidate index as the K dimension in stages of 64.
+// as tcgen05 GEMM tiles of 128 rows x up to 256 channels, the candidate index as the K dimension in stages of 64.
 // A channel tile never crosses a band edge (edges are multiples of 16 channels and a tile is a multiple of 16 wide),
 // so its A operand is a single band's cube. Candidates arrive transposed ([H, R], K-major rows of candidates), the
 // cube through a three-dimensional TMA map.
@@ -9,9 +9,11 @@
 // the same candidate stage, which halves the candidate refills from L2, the traffic this kernel is bound by.
 //
 // Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lanes 32*w..), warp 4 TMA producer, warp 5 UMMA issuer
-// and tensor-memory owner. With `split == 1` each output element is touched by exactly one CTA per launch (plain
-// read-modify-write, deterministic); with a larger split the candidate range is divided and partial sums are added
-// with atomics.
+// and tensor-memory owner. The producer and the issuer run warp-wide with only the TMA / UMMA / commit instructions
+// under the elected lane, so that their operands are warp-uniform values. The epilogue adds its scaled accumulators with
+// vector reductions (fire and forget: no read of the old value comes back to the SM). With `split == 1` each output
+// element receives exactly one addition per launch, so the sum's order is the launches' stream order and the result
+// is deterministic; with a larger split the candidate range is divided and the order of a launch's partial sums is not.
 //
 // Parity: backward_tile_cuda_ (scalingcontrasts.cuh:1042-1136).
 #include <stdexcept>
@@ -27,7 +29,7 @@ namespace {
 
 constexpr uint32_t bwd_rows = 128;
 constexpr uint32_t bwd_depth = 64;        // candidates per stage
-constexpr uint32_t bwd_max_width = 192;   // channels per tile
+constexpr uint32_t bwd_max_width = 256;   // channels per tile
 constexpr uint32_t bwd_stages = 4;                                  // with one row block per CTA; three with two
 constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;        // one 128-row block of the cube
 constexpr uint32_t bwd_b_bytes = bwd_max_width * bwd_depth * 2;
@@ -45,10 +47,18 @@ struct bwd_tail {
     uint32_t abort_flag;
 };
 constexpr uint32_t bwd_shared_bytes = 1024 + 3 * bwd_stage_bytes + sizeof(bwd_tail); // >= 4 * (one block + candidates)
+constexpr uint32_t bwd_candidate_maps = 5;                          // boxes of 16, 32, 64, 128 and 256 channels
 
 struct bwd_tile {
     uint32_t band, channel0, width;
 };
+
+// The transposed candidates under five tensor maps that differ only in the box's channel count (16 << index): a tile's
+// channels are fetched greedily with the largest boxes that fit, so a stage takes one to three candidate loads.
+struct bwd_candidate_boxes {
+    CUtensorMap maps[bwd_candidate_maps];
+};
+
 
 struct bwd_params {
     float* query_gradient;
@@ -62,7 +72,7 @@ struct bwd_params {
 };
 
 __global__ void __launch_bounds__(bwd_threads, 1)
-    backward_kernel(const __grid_constant__ CUtensorMap cube_map, const __grid_constant__ CUtensorMap candidates_map,
+    backward_kernel(const __grid_constant__ CUtensorMap cube_map, const __grid_constant__ bwd_candidate_boxes candidates,
                     const bwd_params p) {
     extern __shared__ uint8_t raw_shared[];
     uint32_t const raw_address = smem_u32(raw_shared);
@@ -98,7 +108,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     }
     if (warp == 4 && lane == 0) {
         tma_prefetch_descriptor(&cube_map);
-        tma_prefetch_descriptor(&candidates_map);
+        for (uint32_t i = 0; i < bwd_candidate_maps; ++i) tma_prefetch_descriptor(&candidates.maps[i]);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -107,47 +117,65 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     wait_context const ctx{p.status, p.budget_ns, &tail->abort_flag};
 
     if (warp == 4) {
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            uint32_t const bytes = blocks * bwd_a_bytes + tile.width * bwd_depth * 2;
-            for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
-                if (!mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_bwd_stage_empty, chunk)) break;
-                uint32_t const full = smem_u32(&tail->stage_full[stage]);
-                uint32_t const destination = stages_base + stage * stage_bytes;
+        bool const elected = elect_one();
+        uint32_t stage = 0, phase = 0;
+        uint32_t const bytes = blocks * bwd_a_bytes + tile.width * bwd_depth * 2;
+        for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_bwd_stage_empty, chunk)))
+                break;
+            uint32_t const full = smem_u32(&tail->stage_full[stage]);
+            uint32_t const destination = stages_base + stage * stage_bytes;
+            if (elected) {
                 mbar_arrive_expect_tx(full, bytes);
                 for (uint32_t block = 0; block < blocks; ++block)
                     tma_load_3d(destination + block * bwd_a_bytes, &cube_map, full, static_cast<int>(chunk * bwd_depth),
                                 static_cast<int>((first_block + block) * bwd_rows), static_cast<int>(tile.band));
-                for (uint32_t r = 0; r < tile.width / 16; ++r)
-                    tma_load_2d(destination + b_offset + r * 2048u, &candidates_map, full,
-                                static_cast<int>(chunk * bwd_depth), static_cast<int>(tile.channel0 + r * 16));
-                if (++stage == stages) stage = 0, phase ^= 1u;
+                // Largest boxes first; 16 channels are 2048 bytes of the stage (rows of 128 bytes under the swizzle).
+                uint32_t done = 0;
+#pragma unroll
+                for (int index = static_cast<int>(bwd_candidate_maps) - 1; index >= 0; --index) {
+                    uint32_t const box = 16u << index;
+                    if (tile.width - done >= box) {
+                        tma_load_2d(destination + b_offset + done * 128u, &candidates.maps[index], full,
+                                    static_cast<int>(chunk * bwd_depth), static_cast<int>(tile.channel0 + done));
+                        done += box;
+                    }
+                }
             }
+            __syncwarp();
+            if (++stage == stages) stage = 0, phase ^= 1u;
         }
     } else if (warp == 5) {
-        if (lane == 0) {
-            uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width);
-            uint32_t stage = 0, phase = 0, accumulate = 0;
-            bool ok = true;
-            for (uint32_t chunk = chunk_begin; chunk < chunk_end && ok; ++chunk) {
-                ok = mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_bwd_stage_full, chunk);
-                if (!ok) break;
-                tcgen05_fence_after();
-                uint32_t const a_address = stages_base + stage * stage_bytes;
-                for (uint32_t block = 0; block < blocks; ++block) {
+        bool const elected = elect_one();
+        uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width);
+        constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
+        uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
+        uint32_t stage = 0, phase = 0, accumulate = 0;
+        bool ok = true;
+        for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tail->stage_full[stage]), phase, ctx, site_bwd_stage_full, chunk));
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t const a_low = low_base + ((stage * stage_bytes) >> 4);
+            uint32_t const b_low = a_low + (b_offset >> 4);
+            for (uint32_t block = 0; block < blocks; ++block) {
 #pragma unroll
-                    for (uint32_t step = 0; step < bwd_depth / 16; ++step)
-                        umma_bf16(tmem_base + block * bwd_block_columns,
-                                  umma_desc_k_major_sw128(a_address + block * bwd_a_bytes + step * 32u, 1024u),
-                                  umma_desc_k_major_sw128(a_address + b_offset + step * 32u, 1024u), idesc,
+                for (uint32_t step = 0; step < bwd_depth / 16; ++step) {
+                    uint64_t a_descriptor, b_descriptor;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(a_descriptor) : "r"(a_low + block * (bwd_a_bytes >> 4) + step * 2u), "r"(descriptor_high));
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(b_descriptor) : "r"(b_low + step * 2u), "r"(descriptor_high));
+                    if (elected)
+                        umma_bf16(tmem_base + block * bwd_block_columns, a_descriptor, b_descriptor, idesc,
                                   step == 0 ? accumulate : 1u);
                 }
-                accumulate = 1;
-                umma_commit(smem_u32(&tail->stage_empty[stage]));
-                if (++stage == stages) stage = 0, phase ^= 1u;
             }
-            if (ok) umma_commit(smem_u32(&tail->accumulated));
+            accumulate = 1;
+            if (elected) umma_commit(smem_u32(&tail->stage_empty[stage]));
+            __syncwarp();
+            if (++stage == stages) stage = 0, phase ^= 1u;
         }
+        if (ok && elected) umma_commit(smem_u32(&tail->accumulated));
+        __syncwarp();
     } else {
         if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.x)) {
             tcgen05_fence_after();
@@ -159,21 +187,12 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                 uint32_t values[16];
                 tmem_load_16(lane_base + column, values);
                 tmem_load_wait();
-                if (p.split == 1) {
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        float4* address = reinterpret_cast<float4*>(destination + column) + v;
-                        float4 current = *address;
-                        current.x = fmaf(p.scale, __uint_as_float(values[4 * v]), current.x);
-                        current.y = fmaf(p.scale, __uint_as_float(values[4 * v + 1]), current.y);
-                        current.z = fmaf(p.scale, __uint_as_float(values[4 * v + 2]), current.z);
-                        current.w = fmaf(p.scale, __uint_as_float(values[4 * v + 3]), current.w);
-                        *address = current;
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) atomicAdd(destination + column + c, p.scale * __uint_as_float(values[c]));
-                }
+                for (int v = 0; v < 4; ++v)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(destination + column + 4 * v),
+                                 "f"(p.scale * __uint_as_float(values[4 * v])), "f"(p.scale * __uint_as_float(values[4 * v + 1])),
+                                 "f"(p.scale * __uint_as_float(values[4 * v + 2])), "f"(p.scale * __uint_as_float(values[4 * v + 3]))
+                                 : "memory");
             }
           }
         }
@@ -228,8 +247,13 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     CUtensorMap const cube_map = encode(a.gradient_cube_bf16, 3, cube_dims, cube_strides, cube_box);
     cuuint64_t const candidate_dims[2] = {a.rows_c, a.hidden};
     cuuint64_t const candidate_strides[1] = {static_cast<cuuint64_t>(a.rows_c) * 2};
-    cuuint32_t const candidate_box[2] = {bwd_depth, 16};
-    CUtensorMap const candidates_map = encode(a.transposed_candidates, 2, candidate_dims, candidate_strides, candidate_box);
+    bwd_candidate_boxes candidates;
+    for (uint32_t index = 0; index < bwd_candidate_maps; ++index) {
+        // A box may not be taller than the tensor; such a box is never asked for either (tiles are at most `hidden` wide).
+        uint32_t const channels = 16u << index;
+        cuuint32_t const candidate_box[2] = {bwd_depth, channels <= a.hidden ? channels : 16u};
+        candidates.maps[index] = encode(a.transposed_candidates, 2, candidate_dims, candidate_strides, candidate_box);
+    }
 
     require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
             "raising the backward kernel's shared memory");
@@ -240,7 +264,7 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     uint32_t const row_blocks = a.rows_q / bwd_rows;
     p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
     dim3 const grid(p.tile_count, (row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, a.split);
-    backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates_map, p);
+    backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("backward launch failed: ") + cudaGetErrorString(error));
     note_launch();

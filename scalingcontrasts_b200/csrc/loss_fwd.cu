@@ -210,15 +210,6 @@ __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::
 // themselves under the elected lane's predicate: loop counters, stage addresses and descriptors are then warp-uniform
 // values the compiler can keep in uniform registers, which is where those instructions take their operands from. (Run
 // by a single lane inside a divergent branch, every operand would cross from a vector to a uniform register first.)
-__device__ __forceinline__ bool elect_one() {
-    uint32_t elected;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xFFFFFFFF;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(elected));
-    return elected != 0u;
-}
 // Every lane waits; the answer is the same in every lane.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
                                                uint32_t detail) {
