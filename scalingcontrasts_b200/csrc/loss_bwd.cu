@@ -83,8 +83,8 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const stages = p.blocks_per_cta == 2 ? 3u : 4u;
     uint32_t const b_offset = p.blocks_per_cta * bwd_a_bytes;
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    bwd_tile const tile = p.tiles[blockIdx.x];
-    uint32_t const first_block = blockIdx.y * p.blocks_per_cta;
+    bwd_tile const tile = p.tiles[blockIdx.y];
+    uint32_t const first_block = blockIdx.x * p.blocks_per_cta;
     uint32_t const blocks = min(p.blocks_per_cta, p.rows_q / bwd_rows - first_block);
     uint32_t const chunks_total = p.rows_c / bwd_depth;
     uint32_t const chunks_per_split = (chunks_total + p.split - 1) / p.split;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
         if (ok && elected) umma_commit(smem_u32(&tail->accumulated));
         __syncwarp();
     } else {
-        if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.x)) {
+        if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.y)) {
             tcgen05_fence_after();
           for (uint32_t block = 0; block < blocks; ++block) {
             uint32_t const row = (first_block + block) * bwd_rows + warp * 32 + lane;
@@ -241,6 +241,14 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
         }
         begin = end;
     }
+    // Widest tiles first, and the grid walks the row blocks fastest: the hardware hands out CTAs in that order, so the
+    // long CTAs start first and the short ones fill the tail, while the tiles that read the same band's cube still run
+    // side by side (same row blocks, same pace) and share it through L2.
+    for (uint32_t i = 1; i < p.tile_count; ++i)
+        for (uint32_t j = i; j > 0 && p.tiles[j - 1].width < p.tiles[j].width; --j) {
+            bwd_tile const held = p.tiles[j - 1];
+            p.tiles[j - 1] = p.tiles[j], p.tiles[j] = held;
+        }
     cuuint64_t const cube_dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
     cuuint64_t const cube_strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
     cuuint32_t const cube_box[3] = {bwd_depth, bwd_rows, 1};
@@ -263,7 +271,7 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
     uint32_t const row_blocks = a.rows_q / bwd_rows;
     p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
-    dim3 const grid(p.tile_count, (row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, a.split);
+    dim3 const grid((row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, p.tile_count, a.split);
     backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("backward launch failed: ") + cudaGetErrorString(error));
