@@ -9,13 +9,17 @@
 // step, so each channel is multiplied exactly once (depth H per cell, where a sweep-and-subtract scheme spends up to
 // 2H). The eight slots form a ring: while the epilogue warps drain the K slots of tile t, the issuing thread already
 // fills the widest bands of tile t+1. The epilogue walks the bands narrowest first, adding each band's segment dots to
-// a running prefix dot in registers, runs the cell math, parks the band's raw-dot gradients in the tensor-memory slot
-// the dots came from, and then walks the bands widest first to form the suffix sums that go to the gradient cube.
+// a running prefix dot in registers, runs the cell math, parks the band's raw-dot gradients (without the factor
+// beta / |q_k| that the row and band share) in the tensor-memory slot the dots came from, and then walks the bands
+// widest first, two at a time, to form the suffix sums that go to the gradient cube. A tile's slots go back to the
+// issuer in two steps: the two widest bands' as soon as the suffix pass has read them (the next tile's narrow bands
+// wait for exactly those slots), the rest when the pass is done.
 //
 // Warp roles (608 threads): warps 0-15 epilogue (warp w owns tensor-memory lanes 32*(w%4).. and the 16 columns w/4 of
 // the tile; four warps per scheduler keep the issue slots busy), warp 16 TMA producer, warp 17 UMMA issuer and
-// tensor-memory owner, warp 18 peer pull (plain 16-byte loads from the peer's replica, plain stores to local staging;
-// never a TMA load from another GPU's memory).
+// tensor-memory owner (both run warp-wide, with the TMA / UMMA / commit instructions under one elected lane), warp 18
+// peer pull (plain 16-byte loads from the peer's replica, plain stores to local staging; never a TMA load from another
+// GPU's memory).
 //
 // A CTA walks work items (row strip, run of consecutive candidate tiles) in a fixed round-robin order and writes one
 // partial record per (run, column quarter, row): the fold over runs happens later in run order, so the loss summands do
@@ -336,9 +340,10 @@ struct tile_cursor {
 };
 
 // Epilogue warps: warp w owns tensor-memory lanes 32*(w%4).. (a quarter of the tile's rows) and the column group w/4 of
-// the tile (16 columns each with sixteen warps). The loop over prefixes is rolled (small code, few registers, four warps per scheduler): a prefix's
-// segment dots come out of tensor memory, its raw-dot gradients go back into the same slot, and a second rolled pass
-// reads them widest first to form the suffix sums. Per-thread sums that are indexed by prefix live in shared memory.
+// the tile (16 columns each with sixteen warps). The loop over prefixes is rolled (small code, few registers, four
+// warps per scheduler): a prefix's segment dots come out of tensor memory, its raw-dot gradients go back into the same
+// slot, and a second rolled pass reads them widest first, in pairs, to form the suffix sums. Per-thread sums that are
+// indexed by prefix live in shared memory.
 template <int prefixes_>
 __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_params const& p, fwd_tail* tail,
                                               uint32_t store_base, float* norm_staging, float* thread_state,
