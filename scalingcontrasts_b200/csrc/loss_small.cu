@@ -181,9 +181,21 @@ __global__ void __launch_bounds__(1024)
     __shared__ float totals[10];
     uint32_t const quantities = 2 + prefixes;
     for (uint32_t quantity = 0; quantity < quantities; ++quantity) {
+        // Four 16-byte loads in flight per thread before anything is added (rows are a multiple of 128, so a quantity's
+        // rows are whole, aligned vectors): one round trip to memory per quantity instead of one per row a thread owns.
         float partial = 0;
-        for (uint32_t row = threadIdx.x; row < rows; row += blockDim.x)
-            partial += accumulators[static_cast<size_t>(quantity) * rows + row];
+        float4 const* const vectors = reinterpret_cast<float4 const*>(accumulators + static_cast<size_t>(quantity) * rows);
+        uint32_t const count = rows / 4;
+        for (uint32_t first = threadIdx.x; first < count; first += 4 * blockDim.x) {
+            float4 held[4];
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                uint32_t const index = first + u * blockDim.x;
+                held[u] = index < count ? vectors[index] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) partial += (held[u].x + held[u].y) + (held[u].z + held[u].w);
+        }
 #pragma unroll
         for (int offset = 16; offset > 0; offset >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, offset);
         if (threadIdx.x % 32 == 0) scratch[threadIdx.x / 32] = partial;
@@ -309,6 +321,8 @@ void launch_finalize(void const* queries_bf16, float const* inverse_norms, float
 
 void launch_sum_summands(float const* row_accumulators, float* summands, uint32_t rows, uint32_t prefixes,
                          cudaStream_t stream) {
+    if (rows % 4 || reinterpret_cast<uintptr_t>(row_accumulators) % 16)
+        throw std::runtime_error("sum_summands: rows must be a multiple of 4 and the accumulators 16-byte aligned");
     sum_summands_kernel<<<1, 1024, 0, stream>>>(row_accumulators, summands, rows, prefixes);
     check_launch("sum_summands");
 }
