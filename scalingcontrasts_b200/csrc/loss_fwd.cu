@@ -420,10 +420,12 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
         uint32_t const column_tile = cursor.column_tile(p);
         uint32_t const column = column_tile * fwd_cols + group * warp_columns;
         float const* const norms_now = staged_norms + buffer * 8 * warp_columns;
-        // Is this a tile where every cell is a plain negative off the cosine floor?
-        uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows;
-        uint64_t const first_column = p.candidate_base + static_cast<uint64_t>(column_tile) * fwd_cols;
-        bool special = first_column < first_row + fwd_rows + 1 && first_row < first_column + fwd_cols + 1;
+        // Is every cell of this warp's patch a plain negative off the cosine floor? The patch is special when its columns
+        // come within one of its rows (a row's own copy, or its pair partner next to it), decided per warp so that a
+        // tile on the diagonal sends only the patches the diagonal crosses through the general cell.
+        uint64_t const first_row = p.query_base + static_cast<uint64_t>(strip) * fwd_rows + quadrant * 32u;
+        uint64_t const first_column = p.candidate_base + column;
+        bool special = first_column < first_row + 32u + 1 && first_row < first_column + warp_columns + 1;
 #pragma unroll
         for (int k = 0; k < prefixes_; ++k) special |= mine[k * fwd_epilogue_threads] * staged_max[buffer * 8 + k] >= 100.0f;
         special = __any_sync(0xFFFFFFFFu, special);
