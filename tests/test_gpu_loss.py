@@ -102,6 +102,31 @@ def test_world_of_two_blocks_against_the_float64_oracle(spec, rows, hidden, pref
     assert float(total[2]) == pytest.approx(expected.log_beta_grad, rel=1e-3, abs=1e-6)
 
 
+@pytest.mark.parametrize("hidden,prefixes,spec", [(128, 2, LossSpec("pairs")), (256, 3, LossSpec("self")), (256, 5, LossSpec("pairs"))],
+                         ids=["K2-pairs", "K3-self", "K5-pairs"])
+def test_many_tiles_per_cta_wrap_the_slot_and_barrier_rings(hidden, prefixes, spec):
+    """4096 rows against themselves: every CTA walks about fourteen tiles, so the eight tensor-memory slots and the eight
+    release barriers wrap several times (with the tile's slot count both dividing eight and not), runs end inside a
+    CTA's walk, and the diagonal crosses 96 tiles. Compared with the float32 statement of the same step."""
+    _float32_matmul_exact()
+    rows = 4096
+    ladder = Matryoshka(tuple(hidden * (k + 1) // prefixes // 16 * 16 for k in range(prefixes)))
+    queries = normal_embeddings(rows, hidden, seed=7, rank=0).cuda()
+    loss = _loss(rows, hidden, ladder, spec)
+    reference = CpuStreamedLoss(rows, hidden, ladder, spec, torch.float32, "cuda")
+    outcomes = []
+    for engine in (loss, reference):
+        engine.begin(queries)
+        engine.score(queries, queries, 0, 0, 10.0, -10.0, rows)
+        gradient, summands = engine.finish(queries)
+        outcomes.append((gradient.float(), summands.double()))
+    torch.cuda.synchronize()
+    loss.check()
+    assert relative_l2(outcomes[0][0], outcomes[1][0]) < 4e-3
+    assert torch.allclose(outcomes[0][1][:3], outcomes[1][1][:3], rtol=2e-4, atol=1e-7)
+    assert torch.allclose(outcomes[0][1][4:4 + prefixes], outcomes[1][1][4:4 + prefixes], rtol=2e-5)
+
+
 def test_block_order_invariance_and_bitwise_repeat():
     ladder = Matryoshka.halvings(256, 3)
     blocks = [normal_embeddings(128, 256, seed=5, rank=r).cuda() for r in range(3)]
