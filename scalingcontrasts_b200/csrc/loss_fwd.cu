@@ -798,7 +798,7 @@ CUtensorMap make_map_2d(void const* base, uint64_t inner, uint64_t outer, uint32
     cuuint32_t const box[2] = {box_inner, box_outer};
     cuuint32_t const element_strides[2] = {1, 1};
     SC_DRIVER(cuTensorMapEncodeTiled, &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return map;
 }
