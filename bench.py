@@ -16,6 +16,13 @@ Two numbers are measured on the same objects: ``value`` times K steps on batches
 ``ContrastiveTrainer.step`` path fed from pinned host memory, with the host-to-device copy of every step's batch and
 the device-to-host read of every step's loss inside the timed region.
 
+Beside the number the line carries its evidence: ``oracle`` (a 128-rows-per-rank step with pair positives over the same
+ranks, run before anything is timed and checked against the float64 evaluation: relative loss and gradient error, ranks
+whose loss bits differ), ``ranks_disagreeing_on_loss`` after the timed steps, ``multicast_kernels`` (which form the
+collective launcher of this process used last), ``loss_step_ms`` / ``loss_ms_per_block`` / ``non_loss_ms`` (the loss
+step timed alone, outside the timed regions), ``clocks`` sampled on every rank through both timed regions, and
+``ms_times_sm_mhz`` so that a power-capped run can be compared with an uncapped one.
+
 ``--impl reference`` is the reference arm. The reference is a C++/CUDA/Mojo tree without a Python package, so it cannot
 be installed into ``baseline/_ref``; the arm prints its ``unavailable`` line.
 """
@@ -92,6 +99,22 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
     ext = _ext.native()  # raises when the extension is missing: no silent fallback
 
+    def fence() -> None:
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    def gather_objects(value):
+        if world == 1:
+            return [value]
+        values = [None] * world
+        dist.all_gather_object(values, value)
+        return values
+
+    # ---- correctness of this job's ranks, before anything is timed -----------------------------------------------
+    oracle_block = small_oracle(rank, world, device, arguments.hidden, arguments.prefixes)
+
     rows, steps, warmup = arguments.rows, arguments.steps, max(arguments.warmup, 3)
     trainer = ContrastiveTrainer(rows, arguments.in_features, arguments.mid_features, arguments.hidden, arguments.prefixes,
                                  device=device, seed=0)
@@ -101,18 +124,12 @@ def main() -> int:
                     for _ in range(rotation)]
     device_batches = [batch.to(device) for batch in host_batches]
 
-    def fence() -> None:
-        torch.cuda.synchronize(device)
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize(device)
-
     # ---- device-timed steps on resident batches ---------------------------------------------------------------
     for step in range(warmup):
         trainer.step_on_device(device_batches[step % rotation])
     fence()
     trainer.check()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    sampler = ClockSampler(local_rank).start()  # every rank samples its own GPU, across both timed regions
     launches_before = ext.launch_count()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -122,9 +139,11 @@ def main() -> int:
     fence()
     elapsed_ms = start.elapsed_time(stop)
     launches = ext.launch_count() - launches_before
-    clocks = sampler.stop() if sampler is not None else None
     trainer.check()
     final_loss = float(trainer.loss.last_summands[0])
+    # every rank must hold the same loss, bit for bit (the summands are all-reduced inside the step)
+    loss_bits = gather_objects(int(trainer.loss.last_summands[0].view(torch.int32).item()))
+    ranks_disagreeing_on_loss = sum(1 for bits in loss_bits if bits != loss_bits[0])
 
     # ---- end to end through the public step(): pinned host batches in, loss out, every step --------------------
     e2e_ms = None
@@ -143,6 +162,22 @@ def main() -> int:
         stop.record()
         fence()
         e2e_ms = start.elapsed_time(stop)
+    clocks = sampler.stop()
+
+    # ---- the loss step alone (outside the timed regions), to separate the blocks' cost from projector and optimizer ----
+    engine = trainer.loss.engine
+    embeddings = trainer.projector(device_batches[0]).detach()
+    for _ in range(3):
+        engine.step(embeddings, scalars=trainer.loss._scalars)
+    fence()
+    loss_steps = max(3, min(steps, 20))
+    start.record()
+    for _ in range(loss_steps):
+        engine.step(embeddings, scalars=trainer.loss._scalars)
+    stop.record()
+    fence()
+    loss_ms = start.elapsed_time(stop) / loss_steps
+    trainer.check()
 
     def reduce_max(value: float) -> float:
         if world == 1:
@@ -152,15 +187,25 @@ def main() -> int:
         return float(tensor.item())
 
     elapsed_ms = reduce_max(elapsed_ms)
+    loss_ms = reduce_max(loss_ms)
     if e2e_ms is not None:
         e2e_ms = reduce_max(e2e_ms)
+    every_clock = gather_objects(clocks)
     cells_per_step_job = world * trainer.cells_per_step()
     value = cells_per_step_job * steps / (elapsed_ms * 1e-3) / 1e9
     uses_multicast = bool(getattr(trainer.domain, "uses_multicast", False))
+    multicast_kernels = ext.last_collective_path() == 1  # what the collective launcher of this process actually used
     if rank == 0:
+        reasons = sorted({reason for record in every_clock for reason in record.get("reasons", [])})
+        medians = [record.get("sm_mhz") for record in every_clock]
+        known = [m for m in medians if m is not None]
+        clock_line = dict(clocks)
+        clock_line.update({"reasons": reasons, "sm_mhz": min(known) if known else None, "sm_mhz_per_rank": medians,
+                           "samples_per_rank": [record.get("samples", 0) for record in every_clock]})
+        ms_per_step = elapsed_ms / steps
         line = {
             "metric": "scored_cells_per_second", "value": round(value, 2), "unit": "Gcells/s", "n_gpus": world,
-            "steps": steps, "warmup": warmup, "ms_per_step": round(elapsed_ms / steps, 4), "higher_is_better": True,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": round(value / (PUBLISHED_GCELLS_PER_GPU * world), 3), "dtype": "bf16",
             "data": "synthetic N(0,1) inputs, random-init (Xavier) weights",
             "impl": "ours",
@@ -177,7 +222,15 @@ def main() -> int:
                 "final_loss": final_loss,
             },
             "gpu_launches": int(launches),
-            "clocks": clocks,
+            "clocks": clock_line,
+            # evidence beside the number: correctness of these ranks, which collective kernels ran, where the time goes
+            "oracle": oracle_block,
+            "ranks_disagreeing_on_loss": ranks_disagreeing_on_loss,
+            "multicast_kernels": multicast_kernels,
+            "loss_step_ms": round(loss_ms, 4),
+            "loss_ms_per_block": round(loss_ms / world, 4),
+            "non_loss_ms": round(ms_per_step - loss_ms, 4),
+            "ms_times_sm_mhz": round(ms_per_step * clock_line["sm_mhz"], 1) if clock_line["sm_mhz"] else None,
         }
         if e2e_ms is not None:
             line["e2e"] = {"value": round(cells_per_step_job * steps / (e2e_ms * 1e-3) / 1e9, 2), "unit": "Gcells/s",
@@ -188,6 +241,50 @@ def main() -> int:
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def small_oracle(rank: int, world: int, device, hidden: int, prefixes: int) -> dict:
+    """One box step of 128 rows per rank with pair positives, checked on rank 0 against the float64 evaluation of the
+    whole world: relative loss error, relative L2 error of all ranks' gradients, and how many ranks hold loss bits that
+    differ from rank 0's. Runs before the timed regions, on a domain of its own."""
+    import torch
+    import torch.distributed as dist
+
+    from scalingcontrasts_b200 import LossSpec, Matryoshka
+    from scalingcontrasts_b200.cpu import oracle, relative_l2
+    from scalingcontrasts_b200.parallel.box import BoxLoss
+    from scalingcontrasts_b200.parallel.domain import Domain
+    from scalingcontrasts_b200.utils.keyed import normal_embeddings
+
+    rows, spec = 128, LossSpec("pairs")
+    ladder = Matryoshka.halvings(hidden, prefixes)
+    domain = Domain.create(payload_scalars=16, heap_bytes=BoxLoss.heap_bytes(rows, hidden, ladder.count), device=device)
+    engine = BoxLoss(rows, hidden, ladder, spec, domain)
+    block = normal_embeddings(rows, hidden, seed=1, rank=rank).to(device)
+    gradient, summands = engine.step(block, 10.0, -10.0)
+    torch.cuda.synchronize(device)
+    engine.check()
+    gradient, summands = gradient.clone(), summands.clone()
+    if world > 1:
+        blocks = [torch.empty_like(block) for _ in range(world)]
+        gradients = [torch.empty_like(gradient) for _ in range(world)]
+        losses = [torch.empty_like(summands) for _ in range(world)]
+        dist.all_gather(blocks, block)
+        dist.all_gather(gradients, gradient)
+        dist.all_gather(losses, summands)
+    else:
+        blocks, gradients, losses = [block], [gradient], [summands]
+    path = domain.collective_path()
+    domain.close()
+    if rank != 0:
+        return {}
+    expected = oracle(torch.cat([b.cpu() for b in blocks]), ladder, 10.0, -10.0, spec)
+    first = int(losses[0][0].view(torch.int32).item())
+    return {"rows_per_rank": rows, "hidden": hidden, "prefixes": list(ladder.ends), "positives": "pairs", "ranks": world,
+            "rel_loss": abs(float(losses[0][0]) - expected.loss) / abs(expected.loss),
+            "rel_grad": float(relative_l2(torch.cat([g.float().cpu() for g in gradients]), expected.gradient)),
+            "ranks_disagreeing": sum(1 for other in losses if int(other[0].view(torch.int32).item()) != first),
+            "collectives": path}
 
 
 if __name__ == "__main__":

@@ -14,8 +14,8 @@ the end:
     box|hosts,R,H,K,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks
     oracle,R,H,K,ranks,exact_loss,measured_loss,rel_grad_err,disagreeing
     barrier,count,stride,min_us,median_us
-    reduce_scatter|all_reduce,count,bytes,min_us,median_us,algbw,busbw
-    validation,count,bytes,wrong_scatter,wrong_sums,repeats,differing
+    reduce_scatter|all_reduce|all_reduce_two_round,count,bytes,min_us,median_us,algbw,busbw,path
+    validation|validation_one_round,count,bytes,wrong_scatter,wrong_sums,repeats,differing,path
     train,R,H,K,world,min_ms,median_ms,gcells_per_s
 
 Multi-GPU modes run one process per GPU. Under ``torchrun`` the ranks are taken from the environment; otherwise the
@@ -70,6 +70,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--steps", type=int, default=defaults.steps)
     parser.add_argument("--device", choices=["cuda", "cpu"], default="cuda")
     parser.add_argument("--no-multicast", action="store_true", help="form a peer domain even where multicast exists")
+    parser.add_argument("--no-graphs", action="store_true", help="enqueue every step kernel by kernel instead of replaying a CUDA graph")
     parser.add_argument("--header", action="store_true")
     return parser
 
@@ -132,7 +133,7 @@ def main(argv: Optional[List[str]] = None) -> int:
 def run(argv: List[str]) -> None:
     arguments = build_parser().parse_args(argv)
     settings = settings_from(arguments)
-    context = RankContext(settings, multicast=not arguments.no_multicast)
+    context = RankContext(settings, multicast=not arguments.no_multicast, graphs=not arguments.no_graphs)
     try:
         if arguments.header and context.rank == 0:
             print(HEADERS[settings.mode], flush=True)
@@ -147,7 +148,7 @@ HEADERS = {
     "box": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks",
     "hosts": "mode,rows,hidden,prefixes,world,bytes,min_ms,median_ms,gcells_per_s_per_gpu,roofline_ms,fraction_of_roofline,peaks",
     "oracle": "mode,rows,hidden,prefixes,ranks,exact_loss,measured_loss,rel_grad_err,disagreeing",
-    "collectives": "mode,count,bytes,min_us,median_us,algbw,busbw",
+    "collectives": "mode,count,bytes,min_us,median_us,algbw,busbw,path",
     "train": "mode,rows,hidden,prefixes,world,min_ms,median_ms,gcells_per_s",
 }
 
@@ -155,11 +156,11 @@ HEADERS = {
 class RankContext:
     """What every mode needs: rank, world, device, an initialised process group when there are several ranks."""
 
-    def __init__(self, settings: Settings, multicast: bool = True) -> None:
+    def __init__(self, settings: Settings, multicast: bool = True, graphs: bool = True) -> None:
         import torch
         import torch.distributed as dist
 
-        self.settings, self.multicast = settings, multicast
+        self.settings, self.multicast, self.graphs = settings, multicast, graphs
         self.rank = int(os.environ.get("RANK", "0"))
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -216,7 +217,9 @@ def _box_engine(context: RankContext):
     ladder.check_device_shape(s.rows, s.hidden)
     domain = Domain.create(payload_scalars=16, heap_bytes=BoxLoss.heap_bytes(s.rows, s.hidden, ladder.count),
                            device=context.device, multicast=context.multicast)
-    return BoxLoss(s.rows, s.hidden, ladder, s.spec(), domain), domain
+    engine = BoxLoss(s.rows, s.hidden, ladder, s.spec(), domain)
+    engine.use_graphs = context.graphs
+    return engine, domain
 
 
 def _roofline_columns(rows: int, world: int, hidden: int, min_ms: float) -> str:
@@ -322,7 +325,7 @@ def run_collectives(context: RankContext) -> None:
     import torch
 
     from ._ext import native
-    from .parallel.domain import Domain
+    from .parallel.domain import Domain, LATENCY_SLOT_BYTES
 
     s = context.settings
     ext = native()
@@ -339,14 +342,18 @@ def run_collectives(context: RankContext) -> None:
     while scalars <= max_scalars:
         shard = scalars // count // 4 * 4
         payload_bytes = shard * count * 4
-        for name, call, factor in (("reduce_scatter", lambda: domain.reduce_scatter(shard), (count - 1) / count),
-                                   ("all_reduce", lambda: domain.all_reduce(shard * count), 2 * (count - 1) / count)):
+        calls = [("reduce_scatter", lambda: domain.reduce_scatter(shard), (count - 1) / count),
+                 ("all_reduce", lambda: domain.all_reduce(shard * count), 2 * (count - 1) / count)]
+        if payload_bytes <= LATENCY_SLOT_BYTES:
+            # the row above took the one-round latency form; this one is the two-round form at the same size
+            calls.append(("all_reduce_two_round", lambda: domain.all_reduce(shard * count, latency=False), 2 * (count - 1) / count))
+        for name, call, factor in calls:
             call()
             context.barrier()
             timing = _time(context, call, s.windows, COLLECTIVE_CALLS)
             algbw = payload_bytes / (timing.min_ms * 1e6)
             context.emit(f"{name},{count},{payload_bytes},{timing.min_ms * 1e3:.2f},{timing.median_ms * 1e3:.2f},"
-                         f"{algbw:.2f},{algbw * factor:.2f}")
+                         f"{algbw:.2f},{algbw * factor:.2f},{domain.collective_path()}")
         scalars *= 2
     domain.check()
     # validation: exact keyed integers, then bit-for-bit repeats of an all-reduce whose sums round
@@ -373,12 +380,33 @@ def run_collectives(context: RankContext) -> None:
             ext.count_differences(payload.data_ptr(), reference.data_ptr(), total, counters.data_ptr() + 16, stream)
     context.barrier()
     domain.check()
-    if context.world > 1:
-        import torch.distributed as dist
+    import torch.distributed as dist
 
+    if context.world > 1:
         dist.all_reduce(counters)
     wrong_scatter, wrong_sums, differing = (int(v) for v in counters.cpu().tolist())
-    context.emit(f"validation,{count},{total * 4},{wrong_scatter},{wrong_sums},{s.repeats},{differing}")
+    context.emit(f"validation,{count},{total * 4},{wrong_scatter},{wrong_sums},{s.repeats},{differing},{domain.collective_path()}")
+    # the same two checks for the one-round latency form, at its largest size
+    small = min(LATENCY_SLOT_BYTES // 4, max_scalars) // 4 * 4
+    counters.zero_()
+    domain.barrier()
+    ext.keyed_integers(payload.data_ptr(), small, 0, count, domain.member, stream)
+    domain.all_reduce(small)
+    ext.count_wrong_sums(payload.data_ptr(), small, 0, count, counters.data_ptr() + 8, stream)
+    for repeat in range(s.repeats):
+        domain.barrier()
+        ext.keyed_fractions(payload.data_ptr(), small, 0, count, domain.member, stream)
+        domain.all_reduce(small)
+        if repeat == 0:
+            reference[:small].copy_(payload[:small])
+        else:
+            ext.count_differences(payload.data_ptr(), reference.data_ptr(), small, counters.data_ptr() + 16, stream)
+    context.barrier()
+    domain.check()
+    if context.world > 1:
+        dist.all_reduce(counters)
+    _, wrong_sums, differing = (int(v) for v in counters.cpu().tolist())
+    context.emit(f"validation_one_round,{count},{small * 4},0,{wrong_sums},{s.repeats},{differing},{domain.collective_path()}")
     domain.close()
 
 
@@ -389,7 +417,7 @@ def run_train(context: RankContext) -> None:
 
     s = context.settings
     trainer = ContrastiveTrainer(s.rows, hidden=s.hidden, prefixes=s.prefixes, spec=s.spec(), device=context.device,
-                                 seed=s.seed, multicast=context.multicast)
+                                 seed=s.seed, multicast=context.multicast, graphs=context.graphs)
     generator = torch.Generator().manual_seed(s.seed * 7919 + context.rank)
     batches = [torch.randn(s.rows, trainer.in_features, generator=generator).to(torch.bfloat16).to(context.device)
                for _ in range(4)]

@@ -47,6 +47,16 @@ void launch_barrier(control_view const& control, cudaStream_t stream);
 // reduced value before it is stored.
 void launch_all_reduce(control_view const& control, void* multicast, void* const* replicas, size_t first,
                        size_t scalars, payload_type type, float scale, int multiprocessors, cudaStream_t stream);
+// The latency form for payloads of at most one staging slot: one arrival round instead of two. `own_payload` is this
+// member's copy of the payload (summed in place, every member computing identical bits); the staging area holds two sets
+// of `members` slots of `slot_bytes` each and is given as its multicast alias (null in a peer domain), every member's
+// copy (peer domain) and this member's copy.
+void launch_all_reduce_small(control_view const& control, void* own_payload, void* multicast_slots, void* const* slot_replicas,
+                             void* own_slots, size_t scalars, payload_type type, float scale, size_t slot_bytes,
+                             cudaStream_t stream);
+// 1 when the last collective launched by this process went through the multicast alias (multimem instructions), 0 when
+// it used peer loads and stores, -1 before the first.
+int last_collective_path();
 // Member m ends with the reduced elements [first + m*shard, first + (m+1)*shard) in its own replica. When
 // `out_f32` is not null the shard goes there instead (as float32, scaled), leaving the payload untouched.
 void launch_reduce_scatter(control_view const& control, void* multicast, void* const* replicas, void* own, size_t first,
@@ -113,11 +123,23 @@ struct forward_arguments {
     // 4 UMMA waiting for a slot, 5 epilogue between tiles, 6 epilogue waiting for a tile, 7 cell pass, 8 suffix pass.
     unsigned long long* trace;
     int multiprocessors;
+    // The fused form: the same launch also folds the gradient patches into `query_gradient` (tensor-core GEMM beside
+    // the scoring), so no gradient cube exists. `gradient_cube_bf16` is then unused; the patches of a work item pass
+    // through `fused_scratch_bf16` (forward_fused_scratch_bytes() bytes, contents meaningless between launches).
+    bool fused;
+    void* fused_scratch_bf16;
+    size_t fused_scratch_bytes;
+    void const* transposed_candidates; // [hidden, rows_c]
+    float* query_gradient;             // [rows_q, hidden], accumulated
+    float gradient_scale;              // the loss passes 2 / live
 };
 // Returns the number of partial slots the launch fills: (column groups per tile) * rows_c / 64 / tiles_per_run.
 uint32_t forward_partial_slots(uint32_t rows_c, uint32_t tiles_per_run);
 uint32_t forward_quantities(uint32_t prefixes);
 uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int multiprocessors);
+bool forward_fused_supported(uint32_t hidden, uint32_t prefixes);
+uint32_t forward_choose_tiles_per_run_fused(uint32_t rows_q, uint32_t rows_c, int multiprocessors);
+size_t forward_fused_scratch_bytes(uint32_t prefixes, uint32_t tiles_per_run, int multiprocessors);
 constexpr int forward_trace_slots = 16;
 void launch_forward(forward_arguments const& arguments, cudaStream_t stream);
 

@@ -70,6 +70,53 @@ std::shared_ptr<control_handle> make_control(sc::native_domain const& domain, ui
     return handle;
 }
 
+// Everything about a streamed-loss object that does not change from block to block, so that scoring a block is one
+// call from Python: the transpose, the tile kernel(s) and the fold of the partial sums are enqueued here back to back.
+struct loss_plan {
+    uint32_t rows_q = 0, rows_c = 0, hidden = 0;
+    sc::ladder_host ladder{};
+    uint32_t tiles_per_run = 1, partial_slots = 0, quantities = 0, backward_split = 1, spec_code = 0;
+    bool fused = false;
+    uint64_t gradients = 0, gradients_bytes = 0; // the gradient cube, or the fused kernel's patch scratch
+    uint64_t transposed = 0, query_gradient = 0, partials = 0, accumulators = 0, status = 0;
+    uint64_t budget_ns = 0;
+    int multiprocessors = 0;
+
+    void score(uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t query_base,
+               uint64_t candidate_base, float beta, float bias, double live, uint64_t scalars, uint64_t pull_src0,
+               uint64_t pull_dst0, uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1,
+               uint64_t stream_handle) const {
+        cudaStream_t const stream = stream_of(stream_handle);
+        sc::launch_transpose(pointer<void>(candidates), pointer<void>(transposed), rows_c, hidden, stream);
+        sc::forward_arguments a{};
+        a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
+        a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
+        a.candidate_tile_max = pointer<float>(c_tile_max);
+        a.gradient_cube_bf16 = pointer<void>(gradients), a.partials = pointer<float>(partials);
+        a.status = pointer<uint32_t>(status);
+        a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder;
+        a.tiles_per_run = tiles_per_run, a.beta = beta, a.bias = bias, a.weight = static_cast<float>(1.0 / live);
+        a.scalars = pointer<float>(scalars);
+        a.query_base = query_base, a.candidate_base = candidate_base, a.spec_code = spec_code, a.budget_ns = budget_ns;
+        a.pull.src[0] = pointer<void>(pull_src0), a.pull.dst[0] = pointer<void>(pull_dst0), a.pull.bytes[0] = pull_bytes0;
+        a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;
+        a.multiprocessors = multiprocessors;
+        a.fused = fused, a.fused_scratch_bf16 = pointer<void>(gradients), a.fused_scratch_bytes = gradients_bytes;
+        a.transposed_candidates = pointer<void>(transposed), a.query_gradient = pointer<float>(query_gradient);
+        a.gradient_scale = static_cast<float>(2.0 / live);
+        sc::launch_forward(a, stream);
+        sc::launch_fold_partials(pointer<float>(partials), pointer<float>(accumulators), rows_q, partial_slots, quantities, stream);
+        if (!fused) {
+            sc::backward_arguments b{};
+            b.gradient_cube_bf16 = pointer<void>(gradients), b.transposed_candidates = pointer<void>(transposed);
+            b.query_gradient = pointer<float>(query_gradient), b.status = pointer<uint32_t>(status);
+            b.rows_q = rows_q, b.rows_c = rows_c, b.hidden = hidden, b.ladder = ladder, b.split = backward_split;
+            b.scale = static_cast<float>(2.0 / live), b.budget_ns = budget_ns;
+            sc::launch_backward(b, stream);
+        }
+    }
+};
+
 torch::Tensor tensor_from_pointer(uint64_t address, std::vector<int64_t> sizes, std::string const& dtype, int device) {
     torch::ScalarType type;
     if (dtype == "float32") type = torch::kFloat32;
@@ -139,6 +186,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         (void)width;
         sc::launch_all_reduce(c.view, multicast, replicas.data(), 0, scalars, kind, scale, sms, stream_of(stream));
     });
+    m.def("all_reduce_small", [](control_handle const& c, uint64_t byte_offset, uint64_t scalars, int type, float scale,
+                                 uint64_t slots_offset, uint64_t slot_bytes, uint64_t stream) {
+        if (byte_offset % 16 || slots_offset % 16) throw std::runtime_error("all_reduce_small: offsets must be multiples of 16");
+        std::vector<void*> slot_replicas;
+        for (void* base : c.replicas) slot_replicas.push_back(static_cast<char*>(base) + slots_offset);
+        void* multicast = c.multicast_base ? pointer<void>(c.multicast_base + slots_offset) : nullptr;
+        sc::launch_all_reduce_small(c.view, pointer<void>(c.own_base + byte_offset), multicast, slot_replicas.data(),
+                                    pointer<void>(c.own_base + slots_offset), scalars, static_cast<sc::payload_type>(type), scale,
+                                    slot_bytes, stream_of(stream));
+    });
+    m.def("last_collective_path", &sc::last_collective_path);
     m.def("reduce_scatter", [](control_handle const& c, uint64_t byte_offset, uint64_t shard_scalars, int type, float scale,
                                uint64_t out_f32, int sms, uint64_t stream) {
         auto const kind = static_cast<sc::payload_type>(type);
@@ -175,9 +233,33 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("sum_summands", [](uint64_t accumulators, uint64_t summands, uint32_t rows, uint32_t prefixes, uint64_t stream) {
         sc::launch_sum_summands(pointer<float>(accumulators), pointer<float>(summands), rows, prefixes, stream_of(stream));
     });
+    py::class_<loss_plan, std::shared_ptr<loss_plan>>(m, "LossPlan")
+        .def(py::init([](uint32_t rows_q, uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends,
+                         uint32_t tiles_per_run, uint32_t partial_slots, uint32_t quantities, uint32_t backward_split,
+                         uint32_t spec_code, bool fused, uint64_t gradients, uint64_t gradients_bytes, uint64_t transposed,
+                         uint64_t query_gradient, uint64_t partials, uint64_t accumulators, uint64_t status,
+                         uint64_t budget_ns, int multiprocessors) {
+                 auto plan = std::make_shared<loss_plan>();
+                 plan->rows_q = rows_q, plan->rows_c = rows_c, plan->hidden = hidden, plan->ladder = ladder_of(ends);
+                 plan->tiles_per_run = tiles_per_run, plan->partial_slots = partial_slots, plan->quantities = quantities;
+                 plan->backward_split = backward_split, plan->spec_code = spec_code, plan->fused = fused;
+                 plan->gradients = gradients, plan->gradients_bytes = gradients_bytes, plan->transposed = transposed;
+                 plan->query_gradient = query_gradient, plan->partials = partials, plan->accumulators = accumulators;
+                 plan->status = status, plan->budget_ns = budget_ns, plan->multiprocessors = multiprocessors;
+                 return plan;
+             }),
+             py::arg("rows_q"), py::arg("rows_c"), py::arg("hidden"), py::arg("ends"), py::arg("tiles_per_run"),
+             py::arg("partial_slots"), py::arg("quantities"), py::arg("backward_split"), py::arg("spec_code"), py::arg("fused"),
+             py::arg("gradients"), py::arg("gradients_bytes"), py::arg("transposed"), py::arg("query_gradient"),
+             py::arg("partials"), py::arg("accumulators"), py::arg("status"), py::arg("budget_ns"), py::arg("multiprocessors"))
+        .def("score", &loss_plan::score);
+    m.def("note_launches", [](uint64_t count) { sc::note_launch(count); });
     m.def("forward_partial_slots", &sc::forward_partial_slots);
     m.def("forward_quantities", &sc::forward_quantities);
     m.def("forward_choose_tiles_per_run", &sc::forward_choose_tiles_per_run);
+    m.def("forward_fused_supported", &sc::forward_fused_supported);
+    m.def("forward_choose_tiles_per_run_fused", &sc::forward_choose_tiles_per_run_fused);
+    m.def("forward_fused_scratch_bytes", &sc::forward_fused_scratch_bytes);
     m.def("forward",
           [](uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t cube,
              uint64_t partials, uint64_t status, uint32_t rows_q, uint32_t rows_c, uint32_t hidden,
@@ -185,7 +267,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              uint64_t query_base,
              uint64_t candidate_base, uint32_t spec_code, uint64_t budget_ns, uint64_t pull_src0, uint64_t pull_dst0,
              uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1, int sms, uint64_t stream,
-             uint64_t trace) {
+             uint64_t trace, bool fused, uint64_t fused_scratch, uint64_t fused_scratch_bytes, uint64_t transposed,
+             uint64_t query_gradient, float gradient_scale) {
               sc::forward_arguments a{};
               a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
               a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
@@ -200,6 +283,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;
               a.multiprocessors = sms;
               a.trace = pointer<unsigned long long>(trace);
+              a.fused = fused, a.fused_scratch_bf16 = pointer<void>(fused_scratch), a.fused_scratch_bytes = fused_scratch_bytes;
+              a.transposed_candidates = pointer<void>(transposed), a.query_gradient = pointer<float>(query_gradient);
+              a.gradient_scale = gradient_scale;
               sc::launch_forward(a, stream_of(stream));
           },
           py::arg("queries"), py::arg("candidates"), py::arg("q_inv"), py::arg("c_inv"), py::arg("c_tile_max"), py::arg("cube"),
@@ -207,7 +293,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("tiles_per_run"), py::arg("beta"), py::arg("bias"), py::arg("weight"), py::arg("scalars"), py::arg("query_base"),
           py::arg("candidate_base"), py::arg("spec_code"), py::arg("budget_ns"), py::arg("pull_src0"), py::arg("pull_dst0"),
           py::arg("pull_bytes0"), py::arg("pull_src1"), py::arg("pull_dst1"), py::arg("pull_bytes1"), py::arg("sms"),
-          py::arg("stream"), py::arg("trace") = 0);
+          py::arg("stream"), py::arg("trace") = 0, py::arg("fused") = false, py::arg("fused_scratch") = 0,
+          py::arg("fused_scratch_bytes") = 0, py::arg("transposed") = 0, py::arg("query_gradient") = 0,
+          py::arg("gradient_scale") = 0.0f);
     m.def("backward", [](uint64_t cube, uint64_t transposed, uint64_t query_gradient, uint64_t status, uint32_t rows_q,
                          uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, float scale,
                          uint64_t budget_ns, uint64_t stream) {

@@ -10,11 +10,19 @@
 // works on its own share, and leaves (every member is done reading), so the kernel's end means the payload is free.
 // The payload may be float32 or bfloat16 (reduced in float32); a scale is folded into the store.
 //
+// Small payloads (up to 64 KiB) have a latency form with ONE arrival round instead of two: every member writes its
+// vector into its own slot of a staging area on every replica (one multimem.st per 16 bytes), arrives once, and then
+// sums the members' slots from its own replica in member order, so every member computes the same bits. The staging
+// area has two sets of slots used alternately (the round's parity), which is what makes the second round unnecessary:
+// a set is rewritten only after a later round that every member joined after it had finished reading.
+//
 // Every wait is bounded: when a member does not show up in time the kernel records status_timeout_collective and
 // returns; later collectives on the same domain return at once.
 //
 // Parity: multimem_barrier_cuda_, multimem_reduce_scatter_cuda_, multimem_all_reduce_cuda_
 // (scalingcontrasts.cuh:142-234) and the Mojo peer_* kernels (scalingcontrasts.mojo:604-729).
+#include <atomic>
+#include <cstdlib>
 #include <stdexcept>
 
 #include "api.h"
@@ -25,7 +33,10 @@ namespace sc {
 namespace {
 
 constexpr int collective_threads = 512;
-constexpr int collective_unroll = 4;
+constexpr int small_threads = 1024;
+
+// Which form the last collective of this process took: 1 multimem (NVSwitch multicast), 0 peer loads and stores.
+std::atomic<int> last_path{-1};
 
 __device__ __forceinline__ void arrive(control_view const& c) {
     if (c.multicast_flag != nullptr) {
@@ -221,7 +232,7 @@ __device__ __forceinline__ vec4 reduce_vector(control_view const& c, char* multi
     }
 }
 
-template <payload_type type_, bool multicast_>
+template <payload_type type_, bool multicast_, int collective_unroll>
 __global__ void __launch_bounds__(collective_threads)
     all_reduce_kernel(control_view c, char* multicast, replica_list replicas, size_t first_vector, size_t vectors,
                       float scale) {
@@ -254,7 +265,7 @@ __global__ void __launch_bounds__(collective_threads)
     leave(c, round);
 }
 
-template <payload_type type_, bool multicast_>
+template <payload_type type_, bool multicast_, int collective_unroll>
 __global__ void __launch_bounds__(collective_threads)
     reduce_scatter_kernel(control_view c, char* multicast, replica_list replicas, char* own, size_t first_vector,
                           size_t shard_vectors, float scale, float* out_f32) {
@@ -292,12 +303,69 @@ __global__ void __launch_bounds__(collective_threads)
     leave(c, round);
 }
 
-int blocks_for(size_t vectors, int multiprocessors) {
-    size_t const per_block = static_cast<size_t>(collective_threads) * collective_unroll;
+// The latency form for small payloads: one block, one arrival round. `own_payload` is this member's payload (read, then
+// overwritten with the sum), `slots` the staging area as seen through the multicast alias (or null), `slot_replicas`
+// every member's staging area (peer form), `own_slots` this member's. Slot (parity, member) starts at
+// (parity * members + member) * slot_bytes.
+template <payload_type type_, bool multicast_>
+__global__ void __launch_bounds__(small_threads)
+    all_reduce_small_kernel(control_view c, char* own_payload, char* slots, replica_list slot_replicas, char* own_slots,
+                            uint32_t vectors, uint32_t slot_bytes, float scale) {
+    __shared__ uint32_t shared_round, shared_ok;
+    if (threadIdx.x == 0) {
+        shared_round = *reinterpret_cast<uint32_t volatile*>(c.own_round);
+        shared_ok = status_poisoned(c.status) ? 0u : 1u;
+    }
+    __syncthreads();
+    if (shared_ok == 0u) return;
+    uint32_t const round = shared_round;
+    uint32_t const parity = (round / c.members) & 1u;
+    size_t const mine = static_cast<size_t>(parity * c.members + c.member) * slot_bytes;
+    for (uint32_t v = threadIdx.x; v < vectors; v += blockDim.x) {
+        vec4 const value = load_vec(own_payload + static_cast<size_t>(v) * 16);
+        if constexpr (multicast_) {
+            multimem_store<payload_type::f32>(slots + mine + static_cast<size_t>(v) * 16, value);
+        } else {
+            for (uint32_t peer = 0; peer < c.members; ++peer)
+                store_vec(static_cast<char*>(slot_replicas.at[peer]) + mine + static_cast<size_t>(v) * 16, value);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        arrive(c);
+        bool const ok = await(c, round + c.members, site_collective_enter);
+        if (ok) *reinterpret_cast<uint32_t volatile*>(c.own_round) = round + c.members;
+        shared_ok = ok ? 1u : 0u;
+    }
+    __syncthreads();
+    if (shared_ok == 0u) return;
+    char const* const first = own_slots + static_cast<size_t>(parity * c.members) * slot_bytes;
+    for (uint32_t v = threadIdx.x; v < vectors; v += blockDim.x) {
+        widened<type_> total = widened<type_>::from(load_vec(first + static_cast<size_t>(v) * 16));
+        for (uint32_t peer = 1; peer < c.members; ++peer)
+            total.add(widened<type_>::from(load_vec(first + static_cast<size_t>(peer) * slot_bytes + static_cast<size_t>(v) * 16)));
+        if (scale != 1.0f) total.scale(scale);
+        store_vec(own_payload + static_cast<size_t>(v) * 16, total.narrow());
+    }
+}
+
+// How a bandwidth-class collective is cut: vectors in flight per thread and the number of blocks. Few, fat blocks win
+// at small sizes (the rounds' bookkeeping is per block), many at large ones. Both can be forced from the environment
+// (SC_COLLECTIVE_UNROLL = 2, 4 or 8; SC_COLLECTIVE_MAX_BLOCKS) to sweep them.
+struct shape_t {
+    int unroll, blocks;
+};
+shape_t shape_for(size_t vectors, int multiprocessors) {
+    static int const forced_unroll = std::getenv("SC_COLLECTIVE_UNROLL") ? std::atoi(std::getenv("SC_COLLECTIVE_UNROLL")) : 0;
+    static int const forced_blocks = std::getenv("SC_COLLECTIVE_MAX_BLOCKS") ? std::atoi(std::getenv("SC_COLLECTIVE_MAX_BLOCKS")) : 0;
+    int unroll = forced_unroll == 2 || forced_unroll == 4 || forced_unroll == 8 ? forced_unroll : 4;
+    int const cap = forced_blocks > 0 ? forced_blocks : multiprocessors;
+    size_t const per_block = static_cast<size_t>(collective_threads) * unroll;
     size_t blocks = (vectors + per_block - 1) / per_block;
     if (blocks < 1) blocks = 1;
-    if (blocks > static_cast<size_t>(multiprocessors)) blocks = static_cast<size_t>(multiprocessors);
-    return static_cast<int>(blocks);
+    if (blocks > static_cast<size_t>(cap)) blocks = static_cast<size_t>(cap);
+    return shape_t{unroll, static_cast<int>(blocks)};
 }
 
 void check_launch(char const* what) {
@@ -315,11 +383,35 @@ replica_list make_list(control_view const& control, void* const* replicas) {
 
 size_t vector_scalars(payload_type type) { return type == payload_type::f32 ? 4 : 8; }
 
+template <payload_type type_, bool multicast_>
+void launch_all_reduce_shape(shape_t shape, control_view const& control, char* mc, replica_list const& list, size_t first_vector,
+                             size_t vectors, float scale, cudaStream_t stream) {
+    if (shape.unroll == 2)
+        all_reduce_kernel<type_, multicast_, 2><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+    else if (shape.unroll == 8)
+        all_reduce_kernel<type_, multicast_, 8><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+    else
+        all_reduce_kernel<type_, multicast_, 4><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+}
+template <payload_type type_, bool multicast_>
+void launch_reduce_scatter_shape(shape_t shape, control_view const& control, char* mc, replica_list const& list, char* mine,
+                                 size_t first_vector, size_t shard_vectors, float scale, float* out_f32, cudaStream_t stream) {
+    if (shape.unroll == 2)
+        reduce_scatter_kernel<type_, multicast_, 2><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+    else if (shape.unroll == 8)
+        reduce_scatter_kernel<type_, multicast_, 8><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+    else
+        reduce_scatter_kernel<type_, multicast_, 4><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+}
+
 } // namespace
+
+int last_collective_path() { return last_path.load(); }
 
 void launch_barrier(control_view const& control, cudaStream_t stream) {
     barrier_kernel<<<1, 32, 0, stream>>>(control);
     check_launch("barrier");
+    last_path.store(control.multicast_flag != nullptr ? 1 : 0);
 }
 
 void launch_expect_arrivals(control_view const& control, uint32_t arrivals, cudaStream_t stream) {
@@ -335,22 +427,46 @@ void launch_all_reduce(control_view const& control, void* multicast, void* const
     if (control.members > 16) throw std::runtime_error("all_reduce: at most 16 members");
     size_t const vectors = scalars / per_vector, first_vector = first / per_vector;
     size_t const share = (vectors + control.members - 1) / control.members;
-    int const blocks = blocks_for(share, multiprocessors);
+    shape_t const shape = shape_for(share, multiprocessors);
     replica_list const list = make_list(control, replicas);
     char* const mc = static_cast<char*>(multicast);
     bool const multicast_path = multicast != nullptr && control.multicast_flag != nullptr;
     if (type == payload_type::f32) {
-        if (multicast_path)
-            all_reduce_kernel<payload_type::f32, true><<<blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
-        else
-            all_reduce_kernel<payload_type::f32, false><<<blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+        if (multicast_path) launch_all_reduce_shape<payload_type::f32, true>(shape, control, mc, list, first_vector, vectors, scale, stream);
+        else launch_all_reduce_shape<payload_type::f32, false>(shape, control, mc, list, first_vector, vectors, scale, stream);
     } else {
-        if (multicast_path)
-            all_reduce_kernel<payload_type::bf16, true><<<blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
-        else
-            all_reduce_kernel<payload_type::bf16, false><<<blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+        if (multicast_path) launch_all_reduce_shape<payload_type::bf16, true>(shape, control, mc, list, first_vector, vectors, scale, stream);
+        else launch_all_reduce_shape<payload_type::bf16, false>(shape, control, mc, list, first_vector, vectors, scale, stream);
     }
     check_launch("all_reduce");
+    last_path.store(multicast_path ? 1 : 0);
+}
+
+void launch_all_reduce_small(control_view const& control, void* own_payload, void* multicast_slots, void* const* slot_replicas,
+                             void* own_slots, size_t scalars, payload_type type, float scale, size_t slot_bytes,
+                             cudaStream_t stream) {
+    size_t const per_vector = vector_scalars(type);
+    if (scalars == 0 || scalars % per_vector) throw std::runtime_error("all_reduce_small: size must be a multiple of one 16-byte vector");
+    size_t const vectors = scalars / per_vector;
+    if (vectors * 16 > slot_bytes || slot_bytes % 16) throw std::runtime_error("all_reduce_small: the payload does not fit a staging slot");
+    if (control.members > 16) throw std::runtime_error("all_reduce_small: at most 16 members");
+    if (own_payload == nullptr || own_slots == nullptr) throw std::runtime_error("all_reduce_small: missing payload or staging area");
+    replica_list const list = make_list(control, slot_replicas);
+    bool const multicast_path = multicast_slots != nullptr && control.multicast_flag != nullptr;
+    int const threads = vectors >= small_threads ? small_threads : static_cast<int>((vectors + 31) / 32 * 32);
+    char* const payload = static_cast<char*>(own_payload);
+    char* const mc = static_cast<char*>(multicast_slots);
+    char* const mine = static_cast<char*>(own_slots);
+    uint32_t const v = static_cast<uint32_t>(vectors), bytes = static_cast<uint32_t>(slot_bytes);
+    if (type == payload_type::f32) {
+        if (multicast_path) all_reduce_small_kernel<payload_type::f32, true><<<1, threads, 0, stream>>>(control, payload, mc, list, mine, v, bytes, scale);
+        else all_reduce_small_kernel<payload_type::f32, false><<<1, threads, 0, stream>>>(control, payload, mc, list, mine, v, bytes, scale);
+    } else {
+        if (multicast_path) all_reduce_small_kernel<payload_type::bf16, true><<<1, threads, 0, stream>>>(control, payload, mc, list, mine, v, bytes, scale);
+        else all_reduce_small_kernel<payload_type::bf16, false><<<1, threads, 0, stream>>>(control, payload, mc, list, mine, v, bytes, scale);
+    }
+    check_launch("all_reduce_small");
+    last_path.store(multicast_path ? 1 : 0);
 }
 
 void launch_reduce_scatter(control_view const& control, void* multicast, void* const* replicas, void* own, size_t first,
@@ -361,23 +477,20 @@ void launch_reduce_scatter(control_view const& control, void* multicast, void* c
         throw std::runtime_error("reduce_scatter: offset and shard must be multiples of one 16-byte vector");
     if (control.members > 16) throw std::runtime_error("reduce_scatter: at most 16 members");
     size_t const shard_vectors = shard_scalars / per_vector, first_vector = first / per_vector;
-    int const blocks = blocks_for(shard_vectors, multiprocessors);
+    shape_t const shape = shape_for(shard_vectors, multiprocessors);
     replica_list const list = make_list(control, replicas);
     char* const mc = static_cast<char*>(multicast);
     char* const mine = static_cast<char*>(own);
     bool const multicast_path = multicast != nullptr && control.multicast_flag != nullptr;
     if (type == payload_type::f32) {
-        if (multicast_path)
-            reduce_scatter_kernel<payload_type::f32, true><<<blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
-        else
-            reduce_scatter_kernel<payload_type::f32, false><<<blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+        if (multicast_path) launch_reduce_scatter_shape<payload_type::f32, true>(shape, control, mc, list, mine, first_vector, shard_vectors, scale, out_f32, stream);
+        else launch_reduce_scatter_shape<payload_type::f32, false>(shape, control, mc, list, mine, first_vector, shard_vectors, scale, out_f32, stream);
     } else {
-        if (multicast_path)
-            reduce_scatter_kernel<payload_type::bf16, true><<<blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
-        else
-            reduce_scatter_kernel<payload_type::bf16, false><<<blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+        if (multicast_path) launch_reduce_scatter_shape<payload_type::bf16, true>(shape, control, mc, list, mine, first_vector, shard_vectors, scale, out_f32, stream);
+        else launch_reduce_scatter_shape<payload_type::bf16, false>(shape, control, mc, list, mine, first_vector, shard_vectors, scale, out_f32, stream);
     }
     check_launch("reduce_scatter");
+    last_path.store(multicast_path ? 1 : 0);
 }
 
 // Loads every collective kernel's code onto the current device while it is idle. A first launch that has to load its
@@ -390,14 +503,26 @@ void preload_collective_kernels() {
     };
     touch(reinterpret_cast<void const*>(&barrier_kernel));
     touch(reinterpret_cast<void const*>(&expect_arrivals_kernel));
-    touch(reinterpret_cast<void const*>(&all_reduce_kernel<payload_type::f32, true>));
-    touch(reinterpret_cast<void const*>(&all_reduce_kernel<payload_type::f32, false>));
-    touch(reinterpret_cast<void const*>(&all_reduce_kernel<payload_type::bf16, true>));
-    touch(reinterpret_cast<void const*>(&all_reduce_kernel<payload_type::bf16, false>));
-    touch(reinterpret_cast<void const*>(&reduce_scatter_kernel<payload_type::f32, true>));
-    touch(reinterpret_cast<void const*>(&reduce_scatter_kernel<payload_type::f32, false>));
-    touch(reinterpret_cast<void const*>(&reduce_scatter_kernel<payload_type::bf16, true>));
-    touch(reinterpret_cast<void const*>(&reduce_scatter_kernel<payload_type::bf16, false>));
+#define SC_TOUCH_SHAPES(kernel)                                                                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 2>));                                           \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 4>));                                           \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 8>));                                           \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, false, 2>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, false, 4>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, false, 8>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, true, 2>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, true, 4>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, true, 8>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, false, 2>));                                         \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, false, 4>));                                         \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, false, 8>));
+    SC_TOUCH_SHAPES(all_reduce_kernel)
+    SC_TOUCH_SHAPES(reduce_scatter_kernel)
+#undef SC_TOUCH_SHAPES
+    touch(reinterpret_cast<void const*>(&all_reduce_small_kernel<payload_type::f32, true>));
+    touch(reinterpret_cast<void const*>(&all_reduce_small_kernel<payload_type::f32, false>));
+    touch(reinterpret_cast<void const*>(&all_reduce_small_kernel<payload_type::bf16, true>));
+    touch(reinterpret_cast<void const*>(&all_reduce_small_kernel<payload_type::bf16, false>));
 }
 
 } // namespace sc

@@ -41,6 +41,11 @@ enum wait_site : uint32_t {
     site_bwd_stage_empty = 21,
     site_bwd_accumulated = 22,
     site_drain = 30,
+    site_fz_item_stored = 40,
+    site_fz_stage_empty = 41,
+    site_fz_stage_full = 42,
+    site_fz_accumulator_empty = 43,
+    site_fz_accumulator_full = 44,
 };
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -95,8 +100,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
+// One attempt that never suspends: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// The same for every state space: orders this thread's view of global memory written by bulk stores with bulk loads
+// that another thread issues after it has been told (through an mbarrier) that the stores are complete.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // The context a bounded wait needs: where to report, how long to wait, and the CTA's abort flag in shared memory.
 struct wait_context {

@@ -46,7 +46,8 @@ struct bwd_tail {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-constexpr uint32_t bwd_shared_bytes = 1024 + 3 * bwd_stage_bytes + sizeof(bwd_tail); // >= 4 * (one block + candidates)
+constexpr uint32_t bwd_shared_bytes = 1024 + 3 * bwd_stage_bytes + sizeof(bwd_tail);
+static_assert(4 * (bwd_a_bytes + bwd_b_bytes) <= 3 * bwd_stage_bytes, "four one-block stages must fit where three two-block stages do");
 constexpr uint32_t bwd_candidate_maps = 5;                          // boxes of 16, 32, 64, 128 and 256 channels
 
 struct bwd_tile {
@@ -78,7 +79,8 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
     bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + 3 * bwd_stage_bytes);
-    // Stage geometry: [row blocks of the cube][candidate tile]; four stages of 40 KB or three of 56 KB.
+    // Stage geometry: [row blocks of the cube][candidate tile]: four stages of 48 KB (one 16 KB row block + 32 KB of
+    // candidates) or three of 64 KB (two row blocks).
     uint32_t const stage_bytes = p.blocks_per_cta * bwd_a_bytes + bwd_b_bytes;
     uint32_t const stages = p.blocks_per_cta == 2 ? 3u : 4u;
     uint32_t const b_offset = p.blocks_per_cta * bwd_a_bytes;
@@ -211,15 +213,6 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     }
 }
 
-CUtensorMap encode(void const* base, uint32_t rank, cuuint64_t const* dims, cuuint64_t const* strides, cuuint32_t const* box) {
-    CUtensorMap map;
-    cuuint32_t const element_strides[3] = {1, 1, 1};
-    SC_DRIVER(cuTensorMapEncodeTiled, &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box,
-              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return map;
-}
-
 } // namespace
 
 void launch_backward(backward_arguments const& a, cudaStream_t stream) {
@@ -252,23 +245,27 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     cuuint64_t const cube_dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
     cuuint64_t const cube_strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
     cuuint32_t const cube_box[3] = {bwd_depth, bwd_rows, 1};
-    CUtensorMap const cube_map = encode(a.gradient_cube_bf16, 3, cube_dims, cube_strides, cube_box);
-    cuuint64_t const candidate_dims[2] = {a.rows_c, a.hidden};
-    cuuint64_t const candidate_strides[1] = {static_cast<cuuint64_t>(a.rows_c) * 2};
+    CUtensorMap const& cube_map = cached_map(a.gradient_cube_bf16, 3, cube_dims, cube_strides, cube_box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     bwd_candidate_boxes candidates;
     for (uint32_t index = 0; index < bwd_candidate_maps; ++index) {
         // A box may not be taller than the tensor; such a box is never asked for either (tiles are at most `hidden` wide).
         uint32_t const channels = 16u << index;
-        cuuint32_t const candidate_box[2] = {bwd_depth, channels <= a.hidden ? channels : 16u};
-        candidates.maps[index] = encode(a.transposed_candidates, 2, candidate_dims, candidate_strides, candidate_box);
+        candidates.maps[index] =
+            cached_operand_map(a.transposed_candidates, a.rows_c, a.hidden, bwd_depth, channels <= a.hidden ? channels : 16u);
     }
 
-    require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
-            "raising the backward kernel's shared memory");
-    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor.
-    int device = 0, multiprocessors = 148;
+    // Per device, once: the shared-memory limit of the kernel and the multiprocessor count.
+    static int prepared_device = -1, multiprocessors = 148;
+    int device = 0;
     cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
+    if (prepared_device != device) {
+        require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
+                "raising the backward kernel's shared memory");
+        cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
+        prepared_device = device;
+    }
+    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor.
     uint32_t const row_blocks = a.rows_q / bwd_rows;
     p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
     dim3 const grid((row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, p.tile_count, a.split);

@@ -42,11 +42,31 @@ constexpr uint32_t fwd_rows = 128;
 constexpr uint32_t fwd_cols = 64;
 constexpr uint32_t fwd_depth = 64;
 constexpr uint32_t fwd_max_stages = 6;
-// Ladders of up to five prefixes leave room for six stages; longer ones keep more per-thread state and get five.
-__host__ __device__ constexpr uint32_t fwd_stages_for(uint32_t prefixes) { return prefixes <= 5 ? 6u : 5u; }
-constexpr uint32_t fwd_slots = 8;
+// Ladders of up to five prefixes leave room for six stages; longer ones keep more per-thread state and get five. The
+// fused kernel shares the shared memory with the gradient GEMM's stages and keeps three.
+__host__ __device__ constexpr uint32_t fwd_stages_for(uint32_t prefixes, bool fused) {
+    return fused ? 3u : (prefixes <= 5 ? 6u : 5u);
+}
+constexpr uint32_t fwd_max_slots = 8;
+// Tensor-memory slots of the score accumulators: all eight 64-column slots, or six when the last 128 columns hold the
+// gradient GEMM's accumulator.
+__host__ __device__ constexpr uint32_t fwd_slots_for(bool fused) { return fused ? 6u : 8u; }
 constexpr uint32_t fwd_slot_columns = 64;
 constexpr uint32_t fwd_tmem_columns = 512;
+// The gradient GEMM that the fused kernel runs beside the scoring: 128 rows x up to 128 channels per accumulator, the
+// candidate index as the K dimension in stages of 64, two stages of [128 rows of the gradient patch | 128 channels of
+// the transposed candidates].
+constexpr uint32_t fz_max_prefixes = 6;
+constexpr uint32_t fz_depth = 64;
+constexpr uint32_t fz_max_width = 128;
+constexpr uint32_t fz_a_bytes = 128 * fz_depth * 2;
+constexpr uint32_t fz_b_bytes = fz_max_width * fz_depth * 2;
+constexpr uint32_t fz_stage_bytes = fz_a_bytes + fz_b_bytes;
+constexpr uint32_t fz_stages = 2;
+constexpr uint32_t fz_accumulator_column = 6 * fwd_slot_columns;
+constexpr uint32_t fz_max_tiles = 48;
+constexpr uint32_t fz_candidate_maps = 4; // boxes of 16, 32, 64 and 128 channels
+constexpr uint32_t fz_max_tiles_per_run = 16;
 #ifndef SC_FWD_EPILOGUE_WARPS
 #define SC_FWD_EPILOGUE_WARPS 16
 #endif
@@ -60,7 +80,10 @@ constexpr uint32_t fwd_producer_warp = fwd_epilogue_warps;
 constexpr uint32_t fwd_mma_warp = fwd_epilogue_warps + 1;
 constexpr uint32_t fwd_first_pull_warp = fwd_epilogue_warps + 2;
 constexpr uint32_t fwd_pull_warps = 1;
-constexpr uint32_t fwd_threads = 32 * (fwd_epilogue_warps + 2 + fwd_pull_warps);
+constexpr uint32_t fz_mma_warp = fwd_epilogue_warps + 3; // fused kernel only; the pull warp doubles as its producer
+__host__ __device__ constexpr uint32_t fwd_threads_for(bool fused) {
+    return 32 * (fwd_epilogue_warps + 2 + fwd_pull_warps + (fused ? 1u : 0u));
+}
 constexpr uint32_t fwd_q_bytes = fwd_rows * fwd_depth * 2;
 constexpr uint32_t fwd_c_bytes = fwd_cols * fwd_depth * 2;
 constexpr uint32_t fwd_stage_bytes = fwd_q_bytes + fwd_c_bytes;
@@ -74,9 +97,16 @@ struct fwd_tail {
     uint64_t stage_empty[fwd_max_stages];
     // Tile t's accumulators have been read by every epilogue warp (index t % fwd_slots): `early` covers the two widest
     // bands, which the suffix pass reads first and whose slots the next tile's UMMAs want first; `late` covers the rest.
-    uint64_t tile_early[fwd_slots];
-    uint64_t tile_late[fwd_slots];
+    uint64_t tile_early[fwd_max_slots];
+    uint64_t tile_late[fwd_max_slots];
     uint64_t tile_full[fwd_tile_barriers];
+    // Fused kernel: the gradient GEMM's stage ring, "this item's gradient patches are in memory" (one per scratch
+    // buffer, an arrival per epilogue warp), and the hand-over of its single accumulator.
+    uint64_t fz_stage_full[fz_stages];
+    uint64_t fz_stage_empty[fz_stages];
+    uint64_t fz_item_stored[2];
+    uint64_t fz_accumulator_full;
+    uint64_t fz_accumulator_empty;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -90,8 +120,12 @@ __host__ __device__ constexpr uint32_t fwd_state_bytes(uint32_t prefixes) { retu
 // column chunks, from which the warp's patches of the gradient cube leave through TMA stores.
 constexpr uint32_t fwd_store_patch_bytes = 32 * fwd_chunk_columns * 2;
 constexpr uint32_t fwd_store_bytes = fwd_epilogue_warps * 2 * fwd_warp_chunks * fwd_store_patch_bytes;
-__host__ __device__ constexpr uint32_t fwd_shared_bytes(uint32_t prefixes) {
-    return 1024 + fwd_stages_for(prefixes) * fwd_stage_bytes + fwd_store_bytes + fwd_tail_bytes + fwd_norm_bytes + fwd_state_bytes(prefixes);
+__host__ __device__ constexpr uint32_t fwd_stage_region_bytes(uint32_t prefixes, bool fused) {
+    return fwd_stages_for(prefixes, fused) * fwd_stage_bytes + (fused ? fz_stages * fz_stage_bytes : 0u);
+}
+__host__ __device__ constexpr uint32_t fwd_shared_bytes(uint32_t prefixes, bool fused) {
+    return 1024 + fwd_stage_region_bytes(prefixes, fused) + fwd_store_bytes + fwd_tail_bytes + fwd_norm_bytes +
+           fwd_state_bytes(prefixes);
 }
 
 struct fwd_params {
@@ -115,6 +149,19 @@ struct fwd_params {
     // downwards, the step is the first of a band (the topmost step, or the step just below a band's first channel).
     // Kept in the kernel's parameters so that the UMMA warp reads it through the uniform datapath. hidden <= 4096.
     uint32_t band_starts[64];
+    // Fused kernel only. The gradient GEMM's channel tiles, one word each: band | first channel / 16 << 4 | width / 16
+    // << 16; a tile never crosses a band edge, so its A operand is one band's patch.
+    float* gradient;       // [rows_q, hidden] float32, accumulated with vector reductions
+    float gradient_scale;  // the loss's 2 / live, applied as the accumulator leaves tensor memory
+    uint32_t tile_count;
+    uint32_t tiles[fz_max_tiles];
+};
+
+// The tensor maps only the fused kernel uses: one over the per-CTA scratch of gradient patches (box of 128 rows x 64
+// candidates, 128-byte swizzle: the GEMM's A operand) and the transposed candidates under boxes of 16 << index channels.
+struct fz_maps {
+    CUtensorMap patches;
+    CUtensorMap candidates[fz_candidate_maps];
 };
 
 // Phase timers, compiled in only with -DSC_FWD_TRACE=1 (a diagnostic build: the clock reads and their branches cost the
@@ -168,8 +215,9 @@ struct row_constants {
 };
 
 // The cell pass leaves each band's raw-dot gradients in tensor memory without the factor beta / |q_k| that is common to
-// the row and the band; the suffix pass multiplies it in while it sums the bands. A row of zero norm has an infinite
-// inverse norm and only zero gradients (its cosines are floored), so the factor is capped to keep 0 * factor at 0.
+// the row and the band; the suffix pass multiplies it in while it sums the bands. The norms kernel writes an inverse
+// norm of 0 for a row of zero norm (factor 0, and its cosines are floored anyway); the cap only keeps a huge inverse
+// norm of a tiny row from turning 0 * factor into a NaN.
 __device__ __forceinline__ float row_factor(float beta, float inv_q) { return beta * fminf(inv_q, 1e30f); }
 
 // Any cell: positives, the diagonal, floored cosines. Only tiles that touch the diagonal or hold a floored norm come here,
@@ -252,9 +300,10 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
     timer.flush(p, 0, 2);
 }
 
-template <int prefixes_>
+template <int prefixes_, bool fused_>
 __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_base, fwd_tail* tail, uint32_t tmem_base,
                                          wait_context const& ctx) {
+    constexpr uint32_t fwd_slots = fwd_slots_for(fused_);
     constexpr uint32_t idesc = umma_idesc_bf16(fwd_rows, fwd_cols);
     constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
     bool const elected = elect_one();
@@ -315,7 +364,7 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
                 }
                 if (elected) umma_commit(smem_u32(&tail->stage_empty[stage]));
                 __syncwarp();
-                if (++stage == fwd_stages_for(prefixes_)) stage = 0, phase ^= 1u;
+                if (++stage == fwd_stages_for(prefixes_, fused_)) stage = 0, phase ^= 1u;
             }
             if (elected) umma_commit(smem_u32(&tail->tile_full[tile_local % fwd_tile_barriers]));
             __syncwarp();
@@ -344,10 +393,29 @@ struct tile_cursor {
 // warps per scheduler): a prefix's segment dots come out of tensor memory, its raw-dot gradients go back into the same
 // slot, and a second rolled pass reads them widest first, in pairs, to form the suffix sums. Per-thread sums that are
 // indexed by prefix live in shared memory.
-template <int prefixes_>
+// Fused kernel: one warp's share of a finished accumulator of the gradient GEMM, added to the owner's rows. The
+// accumulator is [128 rows x width channels]; the warp owns the 32 rows of its lane quadrant and every fourth 16-column
+// chunk, starting at its column group. A real call: the code exists once and the hot loops keep their registers.
+__device__ __noinline__ void fz_drain_chunks(float* destination, uint32_t chunks, uint32_t accumulator, uint32_t group,
+                                             float scale) {
+    for (uint32_t chunk = group; chunk < chunks; chunk += fwd_column_groups) {
+        uint32_t values[16];
+        tmem_load_16(accumulator + chunk * 16u, values);
+        tmem_load_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(destination + chunk * 16u + 4 * v),
+                         "f"(scale * __uint_as_float(values[4 * v])), "f"(scale * __uint_as_float(values[4 * v + 1])),
+                         "f"(scale * __uint_as_float(values[4 * v + 2])), "f"(scale * __uint_as_float(values[4 * v + 3]))
+                         : "memory");
+    }
+}
+
+template <int prefixes_, bool fused_>
 __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_params const& p, fwd_tail* tail,
                                               uint32_t store_base, float* norm_staging, float* thread_state,
                                               uint32_t tmem_base, wait_context const& ctx, uint32_t warp, uint32_t lane) {
+    constexpr uint32_t fwd_slots = fwd_slots_for(fused_);
     constexpr int columns = fwd_chunk_columns;
     constexpr int chunks = fwd_warp_chunks;
     constexpr int warp_columns = fwd_warp_columns;
@@ -401,10 +469,41 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     phase_timer timer(p);
     timer.only_if(threadIdx.x == 0);
 
+    // Fused kernel: the gradient GEMM of a finished item runs on the tensor cores while these warps score the next
+    // item. Its accumulators (one per channel tile, `tile_count` per item, in item order) are drained here: whichever
+    // are ready at the top of a tile, and, before the scratch buffer of item n - 1 is written again by item n + 1,
+    // everything up to item n - 1 (by then long done). `drained` counts the accumulators this warp has taken; the
+    // GEMM does not start accumulator u + 1 before all sixteen warps have taken u, so the barrier's parity is exact.
+    uint32_t items_done = 0, drained = 0;
+    auto drain = [&](uint32_t limit, bool blocking) -> bool {
+        while (drained < limit) {
+            uint32_t const full = smem_u32(&tail->fz_accumulator_full);
+            if (blocking) {
+                if (!mbar_wait(full, drained & 1u, ctx, site_fz_accumulator_full, drained)) return false;
+            } else if (__shfl_sync(0xFFFFFFFFu, mbar_test_wait(full, drained & 1u) ? 1 : 0, 0) == 0) {
+                break;
+            }
+            tcgen05_fence_after();
+            uint32_t const item = blockIdx.x + (drained / p.tile_count) * gridDim.x;
+            uint32_t const word = p.tiles[drained % p.tile_count];
+            float* const destination = p.gradient +
+                                       (static_cast<size_t>(item / p.runs_per_strip) * fwd_rows + row_local) * p.hidden +
+                                       ((word >> 4) & 0xFFFu) * 16u;
+            fz_drain_chunks(destination, word >> 16, tmem_base + ((quadrant * 32u) << 16) + fz_accumulator_column, group,
+                            p.gradient_scale);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tail->fz_accumulator_empty));
+            ++drained;
+        }
+        return true;
+    };
+
     while (cursor.valid(p)) {
         tile_cursor const following = cursor.next(p);
         bool const more = following.valid(p);
         if (more) fetch(following);
+        if constexpr (fused_) drain(items_done * p.tile_count, false);
         uint32_t const strip = cursor.strip, run = cursor.run;
         if (cursor.t == 0) {
             row = strip * fwd_rows + row_local;
@@ -619,13 +718,18 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                              "r"(packed[h][6]), "r"(packed[h][7]) : "memory");
             }
         };
+        // Where the warp's patches go: into the block's gradient cube at the tile's place, or (fused kernel) into this
+        // CTA's scratch buffer of the item, [band][128 rows][tiles_per_run * 64 candidates], at the tile's place in the run.
+        uint32_t const store_x = fused_ ? cursor.t * fwd_cols + group * warp_columns : column;
+        uint32_t const store_y = fused_ ? quadrant * 32u : strip * fwd_rows + quadrant * 32u;
+        uint32_t const store_z = fused_ ? (blockIdx.x * 2u + (items_done & 1u)) * prefixes_ : 0u;
         auto send_patches = [&](uint32_t half, int band) {
 #pragma unroll
             for (int h = 0; h < chunks; ++h)
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                                  reinterpret_cast<uint64_t>(cube_map)),
-                             "r"(warp_store_base + (half * chunks + h) * fwd_store_patch_bytes), "r"(column + h * columns),
-                             "r"(strip * fwd_rows + quadrant * 32u), "r"(band)
+                             "r"(warp_store_base + (half * chunks + h) * fwd_store_patch_bytes), "r"(store_x + h * columns),
+                             "r"(store_y), "r"(store_z + band)
                              : "memory");
         };
         auto release = [&](uint64_t* barriers) {
@@ -692,6 +796,19 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] =
                     2.0f * p.weight * mine[(2 * prefixes_ + k) * fwd_epilogue_threads];
             }
+            if constexpr (fused_) {
+                // The item's patches of this warp are in memory once its bulk stores have completed (not merely been
+                // read out of the staging buffers); then the gradient GEMM's producer may load them.
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    fence_proxy_async_all();
+                    mbar_arrive(smem_u32(&tail->fz_item_stored[items_done & 1u]));
+                }
+                __syncwarp();
+                ++items_done;
+                // The next item writes the other scratch buffer, whose last reader was the GEMM of item items_done - 2.
+                if (!drain((items_done - 1) * p.tile_count, true)) return;
+            }
         }
         cursor = following;
         buffer ^= 1u;
@@ -700,6 +817,100 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
     timer.flush(p, 5, 4);
     // The staging buffers must outlive the stores that read them.
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if constexpr (fused_) drain(items_done * p.tile_count, true);
+}
+
+// ---- fused kernel: the gradient GEMM's two roles ------------------------------------------------------------------
+// For every item this CTA has scored (in the same order), for every channel tile, the K loop over the item's candidates:
+// A = the band's gradient patch [128 rows x 64 candidates] from this CTA's scratch buffer, B = the transposed candidates
+// [width channels x 64 candidates]. Both K-major under the 128-byte swizzle.
+__device__ __forceinline__ void fz_producer_role(fz_maps const* maps, fwd_params const& p, uint32_t stages_base,
+                                                 fwd_tail* tail, wait_context const& ctx, uint32_t const prefixes) {
+    bool const elected = elect_one();
+    uint32_t stage = 0, phase = 0, local = 0;
+    phase_timer timer(p);
+    timer.only_if(elected);
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, ++local) {
+        uint32_t const buffer = local & 1u;
+        timer.lap(0);
+        if (!mbar_wait_warp(smem_u32(&tail->fz_item_stored[buffer]), (local >> 1) & 1u, ctx, site_fz_item_stored, item)) return;
+        timer.lap(1);
+        fence_proxy_async_all();
+        uint32_t const first_candidate = (item % p.runs_per_strip) * p.tiles_per_run * fwd_cols;
+        for (uint32_t which = 0; which < p.tile_count; ++which) {
+            uint32_t const word = p.tiles[which];
+            uint32_t const band = word & 0xFu, channel0 = ((word >> 4) & 0xFFFu) * 16u, width = (word >> 16) * 16u;
+            for (uint32_t block = 0; block < p.tiles_per_run; ++block) {
+                timer.lap(0);
+                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_empty[stage]), phase ^ 1u, ctx, site_fz_stage_empty, which)) return;
+                timer.lap(2);
+                uint32_t const full = smem_u32(&tail->fz_stage_full[stage]);
+                uint32_t const destination = stages_base + stage * fz_stage_bytes;
+                if (elected) {
+                    mbar_arrive_expect_tx(full, fz_a_bytes + width * fz_depth * 2u);
+                    tma_load_3d(destination, &maps->patches, full, static_cast<int>(block * fz_depth), 0,
+                                static_cast<int>((blockIdx.x * 2u + buffer) * prefixes + band));
+                    // Largest boxes first; 16 channels are 2048 bytes of the stage (rows of 128 bytes under the swizzle).
+                    uint32_t done = 0;
+#pragma unroll
+                    for (int index = static_cast<int>(fz_candidate_maps) - 1; index >= 0; --index) {
+                        uint32_t const box = 16u << index;
+                        if (width - done >= box) {
+                            tma_load_2d(destination + fz_a_bytes + done * 128u, &maps->candidates[index], full,
+                                        static_cast<int>(first_candidate + block * fz_depth), static_cast<int>(channel0 + done));
+                            done += box;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (++stage == fz_stages) stage = 0, phase ^= 1u;
+            }
+        }
+    }
+    timer.flush(p, 9, 3);
+}
+
+__device__ __forceinline__ void fz_mma_role(fwd_params const& p, uint32_t stages_base, fwd_tail* tail, uint32_t tmem_base,
+                                            wait_context const& ctx) {
+    constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
+    bool const elected = elect_one();
+    uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
+    uint32_t const accumulator = tmem_base + fz_accumulator_column;
+    uint32_t stage = 0, phase = 0, unit = 0;
+    phase_timer timer(p);
+    timer.only_if(elected);
+    for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {
+        for (uint32_t which = 0; which < p.tile_count; ++which, ++unit) {
+            uint32_t const idesc = umma_idesc_bf16(128, (p.tiles[which] >> 16) * 16u);
+            // The accumulator's previous contents must have left tensor memory (an arrival per epilogue warp).
+            timer.lap(0);
+            if (unit != 0 &&
+                !mbar_wait_warp(smem_u32(&tail->fz_accumulator_empty), (unit - 1) & 1u, ctx, site_fz_accumulator_empty, unit))
+                return;
+            timer.lap(1);
+            tcgen05_fence_after();
+            for (uint32_t block = 0; block < p.tiles_per_run; ++block) {
+                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_full[stage]), phase, ctx, site_fz_stage_full, unit)) return;
+                timer.lap(2);
+                tcgen05_fence_after();
+                uint32_t const a_low = low_base + stage * (fz_stage_bytes >> 4);
+                uint32_t const b_low = a_low + (fz_a_bytes >> 4);
+#pragma unroll
+                for (uint32_t step = 0; step < fz_depth / 16; ++step) {
+                    uint64_t a_descriptor, b_descriptor;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(a_descriptor) : "r"(a_low + step * 2u), "r"(descriptor_high));
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(b_descriptor) : "r"(b_low + step * 2u), "r"(descriptor_high));
+                    if (elected) umma_bf16(accumulator, a_descriptor, b_descriptor, idesc, (block | step) != 0u ? 1u : 0u);
+                }
+                if (elected) umma_commit(smem_u32(&tail->fz_stage_empty[stage]));
+                __syncwarp();
+                if (++stage == fz_stages) stage = 0, phase ^= 1u;
+            }
+            if (elected) umma_commit(smem_u32(&tail->fz_accumulator_full));
+            __syncwarp();
+        }
+    }
+    timer.flush(p, 12, 3);
 }
 
 __device__ __forceinline__ void pull_role(pull_request const& request, uint32_t thread_in_role) {
@@ -722,16 +933,19 @@ __device__ __forceinline__ void pull_role(pull_request const& request, uint32_t 
     }
 }
 
-template <int prefixes_>
-__global__ void __launch_bounds__(fwd_threads, 1)
+template <int prefixes_, bool fused_>
+__global__ void __launch_bounds__(fwd_threads_for(fused_), 1)
     forward_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap c_map,
-                   const __grid_constant__ CUtensorMap cube_map, const fwd_params p) {
+                   const __grid_constant__ CUtensorMap cube_map, const __grid_constant__ fz_maps gemm_maps,
+                   const fwd_params p) {
+    constexpr uint32_t fwd_slots = fwd_slots_for(fused_);
+    constexpr uint32_t stages = fwd_stages_for(prefixes_, fused_);
     extern __shared__ uint8_t raw_shared[];
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
-    fwd_tail* tail =
-        reinterpret_cast<fwd_tail*>(raw_shared + (stages_base - raw_address) + fwd_stages_for(prefixes_) * fwd_stage_bytes +
-                                    fwd_store_bytes);
+    uint32_t const gemm_stages_base = stages_base + stages * fwd_stage_bytes;
+    uint32_t const store_base = stages_base + fwd_stage_region_bytes(prefixes_, fused_);
+    fwd_tail* tail = reinterpret_cast<fwd_tail*>(raw_shared + (store_base - raw_address) + fwd_store_bytes);
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
@@ -745,6 +959,16 @@ __global__ void __launch_bounds__(fwd_threads, 1)
             mbar_init(smem_u32(&tail->tile_late[i]), fwd_epilogue_warps);
         }
         for (uint32_t i = 0; i < fwd_tile_barriers; ++i) mbar_init(smem_u32(&tail->tile_full[i]), 1);
+        if constexpr (fused_) {
+            for (uint32_t i = 0; i < fz_stages; ++i) {
+                mbar_init(smem_u32(&tail->fz_stage_full[i]), 1);
+                mbar_init(smem_u32(&tail->fz_stage_empty[i]), 1);
+            }
+            mbar_init(smem_u32(&tail->fz_item_stored[0]), fwd_epilogue_warps);
+            mbar_init(smem_u32(&tail->fz_item_stored[1]), fwd_epilogue_warps);
+            mbar_init(smem_u32(&tail->fz_accumulator_full), 1);
+            mbar_init(smem_u32(&tail->fz_accumulator_empty), fwd_epilogue_warps);
+        }
         fence_barrier_init();
     }
     __syncthreads();
@@ -757,6 +981,12 @@ __global__ void __launch_bounds__(fwd_threads, 1)
         tma_prefetch_descriptor(&q_map);
         tma_prefetch_descriptor(&c_map);
     }
+    if constexpr (fused_) {
+        if (warp == fwd_first_pull_warp && lane == 0) {
+            tma_prefetch_descriptor(&gemm_maps.patches);
+            for (uint32_t i = 0; i < fz_candidate_maps; ++i) tma_prefetch_descriptor(&gemm_maps.candidates[i]);
+        }
+    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -765,14 +995,19 @@ __global__ void __launch_bounds__(fwd_threads, 1)
 
     if (warp < fwd_epilogue_warps) {
         float* const norm_staging = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tail) + fwd_tail_bytes);
-        epilogue_role<prefixes_>(&cube_map, p, tail, stages_base + fwd_stages_for(prefixes_) * fwd_stage_bytes, norm_staging,
-                                 norm_staging + fwd_norm_bytes / 4, tmem_base, ctx, warp, lane);
+        epilogue_role<prefixes_, fused_>(&cube_map, p, tail, store_base, norm_staging, norm_staging + fwd_norm_bytes / 4,
+                                         tmem_base, ctx, warp, lane);
     } else if (warp == fwd_producer_warp) {
-        producer_role(&q_map, &c_map, p, stages_base, tail, ctx, fwd_stages_for(prefixes_));
+        producer_role(&q_map, &c_map, p, stages_base, tail, ctx, stages);
     } else if (warp == fwd_mma_warp) {
-        mma_role<prefixes_>(p, stages_base, tail, tmem_base, ctx);
-    } else {
+        mma_role<prefixes_, fused_>(p, stages_base, tail, tmem_base, ctx);
+    } else if (warp == fwd_first_pull_warp) {
+        // The pull is a short copy at the start of the launch; the gradient GEMM's first item is not ready before the
+        // epilogue warps have scored a whole item, so the same warp serves both.
         pull_role(p.pull, threadIdx.x - fwd_first_pull_warp * 32);
+        if constexpr (fused_) fz_producer_role(&gemm_maps, p, gemm_stages_base, tail, ctx, prefixes_);
+    } else if (warp == fz_mma_warp) {
+        if constexpr (fused_) fz_mma_role(p, gemm_stages_base, tail, tmem_base, ctx);
     }
 
     tcgen05_fence_before();
@@ -791,25 +1026,45 @@ __global__ void __launch_bounds__(fwd_threads, 1)
 }
 
 // ---- host side --------------------------------------------------------------------------------------------------
-CUtensorMap make_map_2d(void const* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
-    CUtensorMap map;
-    cuuint64_t const dims[2] = {inner, outer};
-    cuuint64_t const strides[1] = {inner * 2};
-    cuuint32_t const box[2] = {box_inner, box_outer};
-    cuuint32_t const element_strides[2] = {1, 1};
-    SC_DRIVER(cuTensorMapEncodeTiled, &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-              element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return map;
+// Rows of `inner` bfloat16 values, `outer` of them, read in boxes under the 128-byte swizzle.
+CUtensorMap const& operand_map(void const* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    return cached_operand_map(base, inner, outer, box_inner, box_outer);
 }
 
-template <int prefixes_>
-void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, CUtensorMap const& cube_map, fwd_params const& p,
-                     int blocks, cudaStream_t stream) {
-    require(cudaFuncSetAttribute(forward_kernel<prefixes_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 fwd_shared_bytes(prefixes_)),
-            "raising the forward kernel's shared memory");
-    forward_kernel<prefixes_><<<blocks, fwd_threads, fwd_shared_bytes(prefixes_), stream>>>(q_map, c_map, cube_map, p);
+template <int prefixes_, bool fused_>
+void launch_instance(CUtensorMap const& q_map, CUtensorMap const& c_map, CUtensorMap const& cube_map, fz_maps const& gemm_maps,
+                     fwd_params const& p, int blocks, cudaStream_t stream) {
+    // The attribute is per device; a process drives one GPU, but a second one costs only the repeat of a cheap call.
+    static int prepared_device = -1;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (prepared_device != device) {
+        require(cudaFuncSetAttribute(forward_kernel<prefixes_, fused_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     fwd_shared_bytes(prefixes_, fused_)),
+                "raising the forward kernel's shared memory");
+        prepared_device = device;
+    }
+    forward_kernel<prefixes_, fused_><<<blocks, fwd_threads_for(fused_), fwd_shared_bytes(prefixes_, fused_), stream>>>(
+        q_map, c_map, cube_map, gemm_maps, p);
+}
+
+template <bool fused_>
+void launch_for_count(uint32_t count, CUtensorMap const& q_map, CUtensorMap const& c_map, CUtensorMap const& cube_map,
+                      fz_maps const& gemm_maps, fwd_params const& p, int blocks, cudaStream_t stream) {
+    switch (count) {
+    case 1: launch_instance<1, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    case 2: launch_instance<2, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    case 3: launch_instance<3, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    case 4: launch_instance<4, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    case 5: launch_instance<5, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    case 6: launch_instance<6, fused_>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream); break;
+    default:
+        if constexpr (!fused_) {
+            if (count == 7) launch_instance<7, false>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream);
+            else launch_instance<8, false>(q_map, c_map, cube_map, gemm_maps, p, blocks, stream);
+        }
+        break;
+    }
 }
 
 } // namespace
@@ -827,17 +1082,37 @@ uint32_t forward_choose_tiles_per_run(uint32_t rows_q, uint32_t rows_c, int mult
     return best;
 }
 
+bool forward_fused_supported(uint32_t hidden, uint32_t prefixes) { return prefixes <= fz_max_prefixes && hidden <= 4096; }
+
+// A fused item is a run of tiles whose gradient patches one GEMM pass folds, adding a [128, hidden] float32 tile to the
+// gradient once per item: runs of at least four tiles keep those additions rare, longer runs are taken while enough
+// items remain to balance the GPU.
+uint32_t forward_choose_tiles_per_run_fused(uint32_t rows_q, uint32_t rows_c, int multiprocessors) {
+    uint32_t const strips = rows_q / fwd_rows, column_tiles = rows_c / fwd_cols;
+    uint32_t best = 1;
+    for (uint32_t t = 1; t <= fz_max_tiles_per_run && column_tiles % t == 0; t *= 2)
+        if (t <= 4 || static_cast<uint64_t>(strips) * (column_tiles / t) >= 6ull * static_cast<uint64_t>(multiprocessors)) best = t;
+    return best;
+}
+
+// Two buffers per CTA of [prefixes][128 rows][tiles_per_run * 64 candidates] bfloat16.
+size_t forward_fused_scratch_bytes(uint32_t prefixes, uint32_t tiles_per_run, int multiprocessors) {
+    return static_cast<size_t>(multiprocessors) * 2 * prefixes * fwd_rows * tiles_per_run * fwd_cols * 2;
+}
+
 void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     if (a.rows_q % fwd_rows || a.rows_c % fwd_cols || a.hidden % fwd_depth || a.hidden > 4096)
         throw std::runtime_error("forward: rows must be multiples of 128 (queries) and 64 (candidates), hidden of 64 up to 4096");
     if (a.ladder.count < 1 || a.ladder.count > 8 || a.ladder.ends[a.ladder.count - 1] != a.hidden)
         throw std::runtime_error("forward: the ladder's widest prefix must equal hidden");
-    for (uint32_t band = 0; band < a.ladder.count; ++band)
-        if (a.ladder.ends[band] % 16) throw std::runtime_error("forward: band edges must be multiples of 16");
+    for (uint32_t band = 0, begin = 0; band < a.ladder.count; begin = a.ladder.ends[band++])
+        if (a.ladder.ends[band] % 16 || a.ladder.ends[band] <= begin)
+            throw std::runtime_error("forward: band edges must ascend in multiples of 16");
     uint32_t const column_tiles = a.rows_c / fwd_cols;
     if (a.tiles_per_run == 0 || column_tiles % a.tiles_per_run)
         throw std::runtime_error("forward: tiles_per_run must divide the number of candidate tiles");
     if (a.pull.bytes[0] % 16 || a.pull.bytes[1] % 16) throw std::runtime_error("forward: pull sizes must be multiples of 16");
+    if (a.multiprocessors < 1) throw std::runtime_error("forward: the multiprocessor count must be positive");
 
     fwd_params p{};
     p.q_inv = a.query_inverse_norms, p.c_inv = a.candidate_inverse_norms, p.c_tile_max = a.candidate_tile_max;
@@ -865,31 +1140,54 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
         }
         p.band_starts[chunk] = word;
     }
-
-    CUtensorMap const q_map = make_map_2d(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
-    CUtensorMap const c_map = make_map_2d(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
-    CUtensorMap cube_map;
-    {
-        cuuint64_t const dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
-        cuuint64_t const strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
-        cuuint32_t const box[3] = {fwd_chunk_columns, 32, 1};
-        cuuint32_t const element_strides[3] = {1, 1, 1};
-        SC_DRIVER(cuTensorMapEncodeTiled, &cube_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.gradient_cube_bf16, dims, strides, box,
-                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    }
     int blocks = static_cast<int>(p.items < static_cast<uint32_t>(a.multiprocessors) ? p.items : a.multiprocessors);
     if ((a.pull.bytes[0] | a.pull.bytes[1]) != 0 && blocks < a.multiprocessors / 2) blocks = a.multiprocessors / 2;
     if (blocks < 1) blocks = 1;
-    switch (a.ladder.count) {
-    case 1: launch_instance<1>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 2: launch_instance<2>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 3: launch_instance<3>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 4: launch_instance<4>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 5: launch_instance<5>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 6: launch_instance<6>(q_map, c_map, cube_map, p, blocks, stream); break;
-    case 7: launch_instance<7>(q_map, c_map, cube_map, p, blocks, stream); break;
-    default: launch_instance<8>(q_map, c_map, cube_map, p, blocks, stream); break;
+
+    CUtensorMap const& q_map = operand_map(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
+    CUtensorMap const& c_map = operand_map(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
+    fz_maps gemm_maps{};
+    if (!a.fused) {
+        // The warps' patches of the gradient cube [K, rows_q, rows_c]: boxes of 32 rows x 16 candidates, unswizzled.
+        cuuint64_t const dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
+        cuuint64_t const strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
+        cuuint32_t const box[3] = {fwd_chunk_columns, 32, 1};
+        CUtensorMap const& cube_map =
+            cached_map(a.gradient_cube_bf16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        launch_for_count<false>(a.ladder.count, q_map, c_map, cube_map, gemm_maps, p, blocks, stream);
+    } else {
+        if (!forward_fused_supported(a.hidden, a.ladder.count))
+            throw std::runtime_error("forward: the fused kernel takes ladders of at most six prefixes");
+        if (a.tiles_per_run > fz_max_tiles_per_run) throw std::runtime_error("forward: a fused run holds at most 16 tiles");
+        if (a.fused_scratch_bytes < forward_fused_scratch_bytes(a.ladder.count, a.tiles_per_run, blocks))
+            throw std::runtime_error("forward: the fused kernel's scratch is too small");
+        if (a.fused_scratch_bf16 == nullptr || a.transposed_candidates == nullptr || a.query_gradient == nullptr)
+            throw std::runtime_error("forward: the fused kernel needs its scratch, the transposed candidates and the gradient");
+        p.gradient = a.query_gradient, p.gradient_scale = a.gradient_scale;
+        for (uint32_t band = 0, begin = 0; band < a.ladder.count; begin = a.ladder.ends[band++])
+            for (uint32_t channel = begin; channel < a.ladder.ends[band]; channel += fz_max_width) {
+                if (p.tile_count == fz_max_tiles) throw std::runtime_error("forward: too many channel tiles for the fused kernel");
+                uint32_t const left = a.ladder.ends[band] - channel;
+                p.tiles[p.tile_count++] = band | ((channel / 16) << 4) | (((left < fz_max_width ? left : fz_max_width) / 16) << 16);
+            }
+        // Scratch of gradient patches: [CTA and buffer][band][128 rows][run of candidates], written in the warps' boxes
+        // (unswizzled), read back as the GEMM's A operand (128 rows x 64 candidates, swizzled).
+        uint64_t const run = static_cast<uint64_t>(a.tiles_per_run) * fwd_cols;
+        cuuint64_t const dims[3] = {run, fwd_rows, static_cast<cuuint64_t>(blocks) * 2 * a.ladder.count};
+        cuuint64_t const strides[2] = {run * 2, run * fwd_rows * 2};
+        cuuint32_t const store_box[3] = {fwd_chunk_columns, 32, 1};
+        cuuint32_t const load_box[3] = {fz_depth, fwd_rows, 1};
+        CUtensorMap const& store_map =
+            cached_map(a.fused_scratch_bf16, 3, dims, strides, store_box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+        gemm_maps.patches =
+            cached_map(a.fused_scratch_bf16, 3, dims, strides, load_box, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        for (uint32_t index = 0; index < fz_candidate_maps; ++index) {
+            // A box may not be taller than the tensor; such a box is never asked for either (tiles are at most `hidden` wide).
+            uint32_t const channels = 16u << index;
+            gemm_maps.candidates[index] =
+                operand_map(a.transposed_candidates, a.rows_c, a.hidden, fz_depth, channels <= a.hidden ? channels : 16u);
+        }
+        launch_for_count<true>(a.ladder.count, q_map, c_map, store_map, gemm_maps, p, blocks, stream);
     }
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("forward launch failed: ") + cudaGetErrorString(error));
@@ -898,14 +1196,20 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
 
 void preload_forward_kernels() {
     cudaFuncAttributes attributes;
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<1>), "preload forward<1>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<2>), "preload forward<2>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<3>), "preload forward<3>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<4>), "preload forward<4>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<5>), "preload forward<5>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<6>), "preload forward<6>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<7>), "preload forward<7>");
-    require(cudaFuncGetAttributes(&attributes, forward_kernel<8>), "preload forward<8>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<1, false>), "preload forward<1>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<2, false>), "preload forward<2>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<3, false>), "preload forward<3>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<4, false>), "preload forward<4>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<5, false>), "preload forward<5>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<6, false>), "preload forward<6>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<7, false>), "preload forward<7>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<8, false>), "preload forward<8>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<1, true>), "preload fused forward<1>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<2, true>), "preload fused forward<2>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<3, true>), "preload fused forward<3>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<4, true>), "preload fused forward<4>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<5, true>), "preload fused forward<5>");
+    require(cudaFuncGetAttributes(&attributes, forward_kernel<6, true>), "preload fused forward<6>");
 }
 
 } // namespace sc

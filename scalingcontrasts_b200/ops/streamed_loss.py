@@ -4,11 +4,16 @@ any order, then ``finish``.
 A rank owns ``rows`` query rows. Each ``score`` runs, on the calling stream,
 
 1. (unless the caller supplies them) the candidates' prefix inverse norms and per-tile maxima,
-2. the forward tile kernel (tcgen05): segment dots of every band in tensor memory, sigmoid loss, per-band
-   suffix-summed gradient cube in bfloat16, per-row partial sums; optionally the same launch pulls the next block from
-   a peer's memory into local staging,
-3. the deterministic fold of the partials,
-4. a transpose of the candidates and the backward tile kernel (tcgen05) that folds the cube into the query gradient.
+2. a transpose of the candidates (the gradient GEMM reads them K-major),
+3. the fused tile kernel (tcgen05): segment dots of every band in tensor memory, sigmoid loss, per-row partial sums, and
+   the per-band suffix-summed gradient of a work item (a strip of 128 rows against a run of candidate tiles) as
+   bfloat16 patches in a per-CTA scratch buffer, which the same CTA folds into the query gradient with a tensor-core
+   GEMM while its epilogue warps already score the next item: no ``[K, R, R]`` gradient cube exists. Optionally the
+   same launch pulls the next block from a peer's memory into local staging,
+4. the deterministic fold of the partials.
+
+Ladders of seven or eight prefixes (or ``fused=False``) take the two-kernel form instead: the forward kernel writes the
+bfloat16 gradient cube ``[K, R, R]`` and a separate backward tile kernel folds it.
 
 ``finish`` folds the L2-normalisation's self term, casts the gradient to bfloat16 and reduces the row summands into
 ``summands`` (any device float32 span of ``SUMMAND_SLOTS`` values, a domain payload included):
@@ -22,6 +27,7 @@ Parity: ``streamed_loss_t`` (scalingcontrasts.cuh:1179-1324) and Mojo ``Streamed
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -98,7 +104,8 @@ class StreamedLoss:
     """One rank's streamed loss state on a GPU. See the module docstring for the contract."""
 
     def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, device=None,
-                 candidate_rows: Optional[int] = None, budget_s: float = 2.0, backward_split: int = 0) -> None:
+                 candidate_rows: Optional[int] = None, budget_s: float = 2.0, backward_split: int = 0,
+                 fused: Optional[bool] = None, tiles_per_run: Optional[int] = None) -> None:
         ladder.check_device_shape(rows, hidden)
         self.rows, self.hidden, self.ladder, self.spec = rows, hidden, ladder, spec
         self.candidate_rows = rows if candidate_rows is None else candidate_rows
@@ -109,7 +116,18 @@ class StreamedLoss:
         properties = torch.cuda.get_device_properties(self.device)
         self.multiprocessors = properties.multi_processor_count
         k, ext = ladder.count, native()
-        self.tiles_per_run = int(ext.forward_choose_tiles_per_run(rows, self.candidate_rows, self.multiprocessors))
+        supported = bool(ext.forward_fused_supported(hidden, k))
+        if fused and not supported:
+            raise ValueError("the fused kernel takes ladders of at most six prefixes")
+        if fused is None and os.environ.get("SC_LOSS_FUSED", "") in ("0", "1"):
+            fused = os.environ["SC_LOSS_FUSED"] == "1" and supported  # A/B switch for measurements
+        self.fused = False if fused is None else bool(fused)
+        chooser = ext.forward_choose_tiles_per_run_fused if self.fused else ext.forward_choose_tiles_per_run
+        self.tiles_per_run = int(chooser(rows, self.candidate_rows, self.multiprocessors))
+        if tiles_per_run is not None:
+            if tiles_per_run < 1 or (self.candidate_rows // 64) % tiles_per_run or (self.fused and tiles_per_run > 16):
+                raise ValueError("tiles_per_run must divide the candidate tiles (and be at most 16 for the fused kernel)")
+            self.tiles_per_run = int(tiles_per_run)
         self.partial_slots = int(ext.forward_partial_slots(self.candidate_rows, self.tiles_per_run))
         self.quantities = int(ext.forward_quantities(k))
         # One CTA per output tile keeps the gradient fold a plain read-modify-write, hence bit-reproducible; a larger
@@ -122,9 +140,21 @@ class StreamedLoss:
         self.query_gradient = torch.zeros(rows, hidden, **f32)
         self.row_accumulators = torch.zeros(self.quantities, rows, **f32)
         self.partials = torch.empty(self.partial_slots, self.quantities, rows, **f32)
-        self.similarity_gradients = torch.empty(k, rows, self.candidate_rows, **bf16)
+        if self.fused:
+            # Gradient patches of the items in flight: two buffers per CTA, independent of the block's size.
+            scratch = int(ext.forward_fused_scratch_bytes(k, self.tiles_per_run, self.multiprocessors))
+            self.similarity_gradients = torch.empty(scratch // 2, **bf16)
+        else:
+            self.similarity_gradients = torch.empty(k, rows, self.candidate_rows, **bf16)
         self.transposed_candidates = torch.empty(hidden, self.candidate_rows, **bf16)
         self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
+        # What never changes between blocks lives in a native plan, so that scoring a block is one call into C++.
+        self._plan = ext.LossPlan(rows, self.candidate_rows, hidden, list(ladder.ends), self.tiles_per_run, self.partial_slots,
+                                  self.quantities, self.backward_split, spec.code(), self.fused,
+                                  self.similarity_gradients.data_ptr(), self.similarity_gradients.numel() * 2,
+                                  self.transposed_candidates.data_ptr(), self.query_gradient.data_ptr(),
+                                  self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.status.data_ptr(),
+                                  self.budget_ns, self.multiprocessors)
         self._begun = False
         self._query_norms_view: Optional[BlockNorms] = None
 
@@ -162,25 +192,15 @@ class StreamedLoss:
         _check_block(candidates)
         if tuple(candidates.shape) != (self.candidate_rows, self.hidden):
             raise ValueError(f"candidates must be [{self.candidate_rows}, {self.hidden}]")
-        ext, s = native(), _stream(stream)
         if candidate_norms is None:
             compute_block_norms(candidates, self.ladder, self.candidate_norms, stream=stream)
             candidate_norms = self.candidate_norms
         pull = pull_next or PullRequest()
         qn = self._query_norms_view
-        ext.forward(queries.data_ptr(), candidates.data_ptr(), qn.inverse.data_ptr(), candidate_norms.inverse.data_ptr(),
-                    candidate_norms.tile_max.data_ptr(), self.similarity_gradients.data_ptr(), self.partials.data_ptr(),
-                    self.status.data_ptr(), self.rows, self.candidate_rows, self.hidden, list(self.ladder.ends),
-                    self.tiles_per_run, float(beta), float(bias), 1.0 / float(live),
-                    0 if scalars is None else scalars.data_ptr(), int(query_base), int(candidate_base), self.spec.code(),
-                    self.budget_ns, pull.src0, pull.dst0, pull.bytes0, pull.src1, pull.dst1, pull.bytes1,
-                    self.multiprocessors, s)
-        ext.fold_partials(self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.rows, self.partial_slots,
-                          self.quantities, s)
-        ext.transpose(candidates.data_ptr(), self.transposed_candidates.data_ptr(), self.candidate_rows, self.hidden, s)
-        ext.backward(self.similarity_gradients.data_ptr(), self.transposed_candidates.data_ptr(),
-                     self.query_gradient.data_ptr(), self.status.data_ptr(), self.rows, self.candidate_rows, self.hidden,
-                     list(self.ladder.ends), self.backward_split, 2.0 / float(live), self.budget_ns, s)
+        self._plan.score(queries.data_ptr(), candidates.data_ptr(), qn.inverse.data_ptr(), candidate_norms.inverse.data_ptr(),
+                         candidate_norms.tile_max.data_ptr(), int(query_base), int(candidate_base), float(beta), float(bias),
+                         float(live), 0 if scalars is None else scalars.data_ptr(), pull.src0, pull.dst0, pull.bytes0,
+                         pull.src1, pull.dst1, pull.bytes1, _stream(stream))
 
     def finish(self, queries: torch.Tensor, gradient_out: Optional[torch.Tensor] = None,
                summands: Optional[torch.Tensor] = None, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -29,6 +29,12 @@ from ..ladder import Matryoshka
 from ..ops.streamed_loss import BlockNorms, PullRequest, StreamedLoss, compute_block_norms
 
 
+def _check_gradient(gradient: torch.Tensor, rows: int, hidden: int) -> None:
+    if (gradient.dtype != torch.bfloat16 or tuple(gradient.shape) != (rows, hidden) or not gradient.is_contiguous()
+            or not gradient.is_cuda):
+        raise ValueError(f"the gradient must be a contiguous CUDA bfloat16 tensor of shape [{rows}, {hidden}]")
+
+
 @dataclass
 class SourceBlock:
     """Where one candidate block lives: in this GPU's memory (``embeddings`` / ``norms`` given), or in a domain member's
@@ -75,6 +81,8 @@ class BoxLoss:
         self.staged = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
         self.staged_norms = [BlockNorms(k, rows, device=self.device) for _ in range(2)]
         self.gradient = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device)
+        self.use_graphs = False
+        self._graphs = {}
 
     @staticmethod
     def heap_bytes(rows: int, hidden: int, prefixes: int) -> int:
@@ -112,12 +120,11 @@ class BoxLoss:
                             candidate_norms=norms, scalars=scalars, pull_next=pull)
 
     # ------------------------------------------------------------------------------------------------------
-    def step(self, queries: torch.Tensor, beta: float = 10.0, bias: float = -10.0, scalars: Optional[torch.Tensor] = None,
-             gradient_out: Optional[torch.Tensor] = None, stream=None, reduce: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Runs one step; returns ``(gradient [R,H] bf16, summands [SUMMAND_SLOTS] f32)``. With ``reduce`` the summands
-        are the world's sums on return (stream order)."""
+    def _core(self, beta: float, bias: float, scalars: Optional[torch.Tensor], gradient: torch.Tensor, reduce: bool,
+              stream) -> None:
+        """Everything of a step after the publish pass. It touches only buffers this object (or its domain) owns plus
+        ``scalars`` and ``gradient``, which is what makes it replayable as a CUDA graph."""
         members, member, rows = self.members, self.member, self.rows
-        compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
         if self.domain is not None:
             self.domain.barrier(stream)
         self.loss.begin(self.embeddings, stream, query_norms=self.norms)
@@ -127,11 +134,60 @@ class BoxLoss:
             blocks.append(SourceBlock(peer * rows, member=peer, embeddings_offset=self._embeddings_offset,
                                       norms_offset=self._norms_offset))
         self.score_sequence(blocks, member * rows, members * rows, beta, bias, scalars, stream)
-        gradient = self.gradient if gradient_out is None else gradient_out
         self.loss.finish(self.embeddings, gradient, self.summands, stream)
-        if reduce and self.domain is not None:
-            self.domain.all_reduce(SUMMAND_SLOTS, stream)
+        if self.domain is not None:
+            # Either collective closes the step: its rounds are also the fence that says "every peer has finished
+            # reading my block", without which the next step's publish could overwrite a block still being pulled.
+            if reduce:
+                self.domain.all_reduce(SUMMAND_SLOTS, stream)
+            else:
+                self.domain.barrier(stream)
+
+    def step(self, queries: torch.Tensor, beta: float = 10.0, bias: float = -10.0, scalars: Optional[torch.Tensor] = None,
+             gradient_out: Optional[torch.Tensor] = None, stream=None, reduce: bool = True,
+             graph: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Runs one step; returns ``(gradient [R,H] bf16, summands [SUMMAND_SLOTS] f32)``. With ``reduce`` the summands
+        are the world's sums on return (stream order); without it they are this rank's share and a barrier closes the
+        step instead.
+
+        With ``graph`` (default: the object's ``use_graphs``) everything after the publish pass is captured once per
+        argument set as a CUDA graph and replayed afterwards, so a step costs the host two launches however many
+        blocks it scores; the first call of an argument set runs eagerly, the second captures. Every member of the
+        domain must make the same choice in the same step."""
+        compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
+        gradient = self.gradient if gradient_out is None else gradient_out
+        _check_gradient(gradient, self.rows, self.hidden)
+        if (self.use_graphs if graph is None else graph) and stream is None:
+            self._replay(float(beta), float(bias), scalars, gradient, bool(reduce))
+        else:
+            self._core(beta, bias, scalars, gradient, reduce, stream)
         return gradient, self.summands
+
+    def _replay(self, beta: float, bias: float, scalars: Optional[torch.Tensor], gradient: torch.Tensor, reduce: bool) -> None:
+        from .._ext import native
+
+        key = (beta, bias, 0 if scalars is None else scalars.data_ptr(), gradient.data_ptr(), reduce)
+        entry = self._graphs.get(key)
+        if entry is None:
+            # First use: run eagerly (loads every kernel, fills the tensor-map cache) and remember that it happened.
+            self._core(beta, bias, scalars, gradient, reduce, None)
+            if len(self._graphs) >= 8:
+                self._graphs.clear()
+            self._graphs[key] = False
+            return
+        if entry is False:
+            ext = native()
+            graph = torch.cuda.CUDAGraph()
+            before = ext.launch_count()
+            with torch.cuda.graph(graph):
+                self._core(beta, bias, scalars, gradient, reduce, None)
+            # The launchers counted their kernels while capturing, although nothing ran: that count stands for the replay
+            # that follows, and later replays add it themselves. `scalars` and `gradient` are kept alive with the graph.
+            self._graphs[key] = (graph, int(ext.launch_count() - before), scalars, gradient)
+            graph.replay()
+            return
+        entry[0].replay()
+        native().note_launches(entry[1])
 
     def simulate(self, queries: torch.Tensor, world: int, beta: float = 10.0, bias: float = -10.0, stream=None,
                  pull: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -33,6 +33,8 @@ import torch
 from .._ext import native
 
 CONTROL_REGION = 4096  # bytes reserved at the start of every replica for the control block
+LATENCY_SLOT_BYTES = 64 << 10  # largest payload of the one-round all-reduce
+LATENCY_CHANNELS = 4  # control channels that own a staging area for it
 _TYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
 _DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16", torch.int32: "int32", torch.uint8: "uint8",
                 torch.int64: "int64"}
@@ -226,7 +228,10 @@ class DeviceDomain(Domain):
         ext = native()
         rendezvous = StoreRendezvous(group)
         payload_bytes = -(-payload_scalars * 4 // 256) * 256
-        total = CONTROL_REGION + payload_bytes + int(heap_bytes)
+        heap_end = CONTROL_REGION + payload_bytes + int(heap_bytes)
+        heap_end = -(-heap_end // 256) * 256
+        # Staging area of the one-round all-reduce: per channel two sets (used alternately) of one slot per member.
+        total = heap_end + LATENCY_CHANNELS * 2 * rendezvous.world * LATENCY_SLOT_BYTES
         index = device.index if device.index is not None else torch.cuda.current_device()
         torch.cuda.set_device(index)
         supported = bool(ext.NativeDomain.multicast_supported(index)) if want_multicast else False
@@ -296,7 +301,8 @@ class DeviceDomain(Domain):
         domain.payload_scalars = payload_scalars
         domain._payload_offset = CONTROL_REGION
         domain._heap_next = CONTROL_REGION + payload_bytes
-        domain._heap_end = total
+        domain._heap_end = heap_end
+        domain._latency_offset = heap_end
         domain.budget_s = default_budget_s() if budget_s is None else budget_s
         domain._control = ext.make_control(handle, 0, int(domain.budget_s * 1e9), domain.uses_multicast)
         domain._channels = {0: domain._control}
@@ -353,11 +359,25 @@ class DeviceDomain(Domain):
         native().barrier(self.channel(channel), self._stream(stream))
 
     def all_reduce(self, scalars: Optional[int] = None, stream=None, *, offset: Optional[int] = None,
-                   dtype: torch.dtype = torch.float32, scale: float = 1.0, channel: int = 0) -> None:
-        """In place over the first ``scalars`` elements of the payload (or of the heap region at ``offset``)."""
+                   dtype: torch.dtype = torch.float32, scale: float = 1.0, channel: int = 0,
+                   latency: Optional[bool] = None) -> None:
+        """In place over the first ``scalars`` elements of the payload (or of the heap region at ``offset``). Payloads
+        of up to 64 KiB take the one-round latency form (every member sums the members' staged vectors itself, in
+        member order) unless ``latency`` is False; larger ones are reduced and broadcast by the switch in two rounds."""
         scalars = self.payload_scalars if scalars is None else scalars
-        native().all_reduce(self.channel(channel), self._payload_offset if offset is None else offset, scalars,
-                            _TYPE_CODES[dtype], float(scale), self.multiprocessors, self._stream(stream))
+        byte_offset = self._payload_offset if offset is None else offset
+        nbytes = scalars * (4 if dtype == torch.float32 else 2)
+        if nbytes <= LATENCY_SLOT_BYTES and channel < LATENCY_CHANNELS and latency is not False:
+            slots = self._latency_offset + channel * 2 * self.members * LATENCY_SLOT_BYTES
+            native().all_reduce_small(self.channel(channel), byte_offset, scalars, _TYPE_CODES[dtype], float(scale), slots,
+                                      LATENCY_SLOT_BYTES, self._stream(stream))
+            return
+        native().all_reduce(self.channel(channel), byte_offset, scalars, _TYPE_CODES[dtype], float(scale),
+                            self.multiprocessors, self._stream(stream))
+
+    def collective_path(self) -> str:
+        """How the last collective launched by this process reached its peers: ``multimem`` or ``peer``."""
+        return {1: "multimem", 0: "peer"}.get(int(native().last_collective_path()), "none")
 
     def reduce_scatter(self, shard_scalars: int, stream=None, *, offset: Optional[int] = None,
                        dtype: torch.dtype = torch.float32, scale: float = 1.0, out: Optional[torch.Tensor] = None,

@@ -26,7 +26,7 @@ from .parallel.reducer import GradientReducer
 class ContrastiveTrainer:
     def __init__(self, rows: int, in_features: int = 1024, mid_features: int = 3072, hidden: int = 768, prefixes: int = 5,
                  spec: LossSpec = REFERENCE_SPEC, lr: float = 1e-4, weight_decay: float = 0.0, group=None, device=None,
-                 seed: int = 0, multicast: Optional[bool] = None, optimizer: str = "adamw") -> None:
+                 seed: int = 0, multicast: Optional[bool] = None, optimizer: str = "adamw", graphs: bool = True) -> None:
         from .parallel.box import BoxLoss
         from .parallel.domain import Domain
 
@@ -38,6 +38,9 @@ class ContrastiveTrainer:
         self.domain = Domain.create(payload_scalars=16, heap_bytes=heap, group=group, device=self.device, multicast=multicast)
         self.world, self.rank = self.domain.members, self.domain.member
         self.loss = MatryoshkaSigmoidLoss(rows, hidden, prefixes, self.ladder, spec, self.domain, group, self.device)
+        # The loss step after its publish pass is the same kernel sequence over the same buffers every time: replayed as
+        # a CUDA graph it costs the host two launches however many peers are scored.
+        self.loss.engine.use_graphs = graphs
         # Every rank's loss is the world's sum and row gradients are final, so parameter gradients are summed.
         self.reducer = GradientReducer(self.projector.parameters(), self.domain, scale=1.0)
         parameters = list(self.projector.parameters()) + list(self.loss.parameters())

@@ -51,6 +51,28 @@ def test_world_of_one_collectives(domains, ext, multicast):
     domain.check()
 
 
+@pytest.mark.parametrize("multicast", [True, False])
+def test_one_round_and_two_round_all_reduce_agree(domains, multicast):
+    """Payloads of up to 64 KiB take the one-round latency form by default; forced through the two-round form they must
+    give the same bits, at the largest such size and at a few vectors, in float32 and in bfloat16 with a scale."""
+    from scalingcontrasts_b200.utils.keyed import keyed_fractions
+
+    domain = domains[multicast]
+    payload = domain.payload()
+    values = keyed_fractions(1 << 14, 1, 3).cuda()
+    for scalars in (1 << 14, 12 * 4, 4):
+        outcomes = []
+        for latency in (None, False, None):  # one-round twice in a row: both sets of staging slots get used
+            payload[:1 << 14].copy_(values)
+            domain.all_reduce(scalars, scale=0.25, latency=latency)
+            torch.cuda.synchronize()
+            outcomes.append(payload[:1 << 14].clone())
+        assert torch.equal(outcomes[0], outcomes[1]) and torch.equal(outcomes[0], outcomes[2])
+        assert torch.equal(outcomes[0][:scalars], values[:scalars] * 0.25) and torch.equal(outcomes[0][scalars:], values[scalars:])
+    domain.check()
+    assert domain.collective_path() in ("multimem", "peer")
+
+
 def test_bounded_wait_reports_and_recovers(domains):
     from scalingcontrasts_b200.parallel.domain import DomainError
 

@@ -9,10 +9,10 @@ from scalingcontrasts_b200.utils.keyed import keyed_embeddings, normal_embedding
 pytestmark = pytest.mark.gpu
 
 
-def _loss(rows, hidden, ladder, spec=LossSpec("self")):
+def _loss(rows, hidden, ladder, spec=LossSpec("self"), fused=None):
     from scalingcontrasts_b200.ops.streamed_loss import StreamedLoss
 
-    return StreamedLoss(rows, hidden, ladder, spec, "cuda")
+    return StreamedLoss(rows, hidden, ladder, spec, "cuda", fused=fused)
 
 
 def _float32_matmul_exact():
@@ -46,7 +46,7 @@ def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefi
     ladder = Matryoshka.halvings(hidden, prefixes)
     queries = normal_embeddings(rows, hidden, seed=1, rank=0).cuda()
     candidates = normal_embeddings(rows, hidden, seed=1, rank=1).cuda()
-    loss = _loss(rows, hidden, ladder)
+    loss = _loss(rows, hidden, ladder, fused=False)
     loss.begin(queries)
     loss.score(queries, candidates, 0, rows, 10.0, -10.0, 2 * rows)
     torch.cuda.synchronize()
@@ -74,16 +74,19 @@ def test_forward_cube_and_backward_fold_against_float32(ext, rows, hidden, prefi
 @pytest.mark.parametrize("spec", [LossSpec("self"), LossSpec("pairs"), LossSpec("pairs", "skip")],
                          ids=lambda s: f"{s.positives}-{s.diagonal}")
 @pytest.mark.parametrize("rows,hidden,prefixes,kind", [(128, 256, 3, "normal"), (128, 768, 5, "normal"), (256, 768, 5, "keyed")])
-def test_world_of_two_blocks_against_the_float64_oracle(spec, rows, hidden, prefixes, kind):
+@pytest.mark.parametrize("fused", [False, True], ids=["two-kernel", "fused"])
+def test_world_of_two_blocks_against_the_float64_oracle(spec, rows, hidden, prefixes, kind, fused):
     """One GPU plays both ranks of a two-rank world in turn; loss, per-prefix losses, gradients and the two scalar
-    gradients are compared with the float64 evaluation of the whole world."""
+    gradients are compared with the float64 evaluation of the whole world. Both forms of the tile kernels are held to
+    the same tolerances: the forward kernel with a gradient cube and a backward kernel, and the fused kernel that folds
+    the gradient itself."""
     ladder = Matryoshka.halvings(hidden, prefixes)
     if kind == "normal":
         blocks = [normal_embeddings(rows, hidden, seed=1, rank=r).cuda() for r in range(2)]
     else:
         blocks = [keyed_embeddings(rows, hidden, r, 1.0).cuda() for r in range(2)]
     expected = oracle(torch.cat(blocks).cpu(), ladder, 10.0, -10.0, spec)
-    loss = _loss(rows, hidden, ladder, spec)
+    loss = _loss(rows, hidden, ladder, spec, fused=fused)
     total = torch.zeros(12, dtype=torch.float64)
     gradients = []
     for rank in range(2):
@@ -102,17 +105,21 @@ def test_world_of_two_blocks_against_the_float64_oracle(spec, rows, hidden, pref
     assert float(total[2]) == pytest.approx(expected.log_beta_grad, rel=1e-3, abs=1e-6)
 
 
-@pytest.mark.parametrize("hidden,prefixes,spec", [(128, 2, LossSpec("pairs")), (256, 3, LossSpec("self")), (256, 5, LossSpec("pairs"))],
-                         ids=["K2-pairs", "K3-self", "K5-pairs"])
-def test_many_tiles_per_cta_wrap_the_slot_and_barrier_rings(hidden, prefixes, spec):
+@pytest.mark.parametrize("hidden,prefixes,spec", [(128, 2, LossSpec("pairs")), (256, 3, LossSpec("self")), (256, 5, LossSpec("pairs")),
+                                                  (768, 5, LossSpec("pairs")), (384, 6, LossSpec("self"))],
+                         ids=["K2-pairs", "K3-self", "K5-pairs", "H768-K5-pairs", "K6-self"])
+@pytest.mark.parametrize("fused", [False, True], ids=["two-kernel", "fused"])
+def test_many_tiles_per_cta_wrap_the_slot_and_barrier_rings(hidden, prefixes, spec, fused):
     """4096 rows against themselves: every CTA walks about fourteen tiles, so the eight tensor-memory slots and the eight
     release barriers wrap several times (with the tile's slot count both dividing eight and not), runs end inside a
     CTA's walk, and the diagonal crosses 96 tiles. Compared with the float32 statement of the same step."""
     _float32_matmul_exact()
     rows = 4096
-    ladder = Matryoshka(tuple(hidden * (k + 1) // prefixes // 16 * 16 for k in range(prefixes)))
+    ladder = (Matryoshka.halvings(hidden, prefixes) if hidden == 768 else
+              Matryoshka(tuple(hidden * (k + 1) // prefixes // 16 * 16 for k in range(prefixes))))
     queries = normal_embeddings(rows, hidden, seed=7, rank=0).cuda()
-    loss = _loss(rows, hidden, ladder, spec)
+    loss = _loss(rows, hidden, ladder, spec, fused=fused)
+    assert loss.fused == fused
     reference = CpuStreamedLoss(rows, hidden, ladder, spec, torch.float32, "cuda")
     outcomes = []
     for engine in (loss, reference):
@@ -125,6 +132,29 @@ def test_many_tiles_per_cta_wrap_the_slot_and_barrier_rings(hidden, prefixes, sp
     assert relative_l2(outcomes[0][0], outcomes[1][0]) < 4e-3
     assert torch.allclose(outcomes[0][1][:3], outcomes[1][1][:3], rtol=2e-4, atol=1e-7)
     assert torch.allclose(outcomes[0][1][4:4 + prefixes], outcomes[1][1][4:4 + prefixes], rtol=2e-5)
+
+
+@pytest.mark.parametrize("fused", [False, True], ids=["two-kernel", "fused"])
+def test_runs_of_one_tile_and_of_several_agree(fused):
+    """A CTA's work item is a run of candidate tiles whose per-row sums leave as one record. Runs of four tiles and runs
+    of one tile must give the same step (the fold over records is a float32 sum, so: to rounding)."""
+    from scalingcontrasts_b200.ops.streamed_loss import StreamedLoss
+
+    rows, hidden = 2048, 256
+    ladder = Matryoshka.halvings(hidden, 3)
+    queries = normal_embeddings(rows, hidden, seed=11, rank=0).cuda()
+    outcomes = []
+    for forced in (4, 1):
+        loss = StreamedLoss(rows, hidden, ladder, LossSpec("pairs"), "cuda", fused=fused, tiles_per_run=forced)
+        assert loss.tiles_per_run == forced
+        loss.begin(queries)
+        loss.score(queries, queries, 0, 0, 10.0, -10.0, rows)
+        gradient, summands = loss.finish(queries)
+        torch.cuda.synchronize()
+        loss.check()
+        outcomes.append((gradient.float(), summands.double()))
+    assert relative_l2(outcomes[0][0], outcomes[1][0]) < 1e-3
+    assert torch.allclose(outcomes[0][1], outcomes[1][1], rtol=1e-5, atol=1e-9)
 
 
 def test_block_order_invariance_and_bitwise_repeat():

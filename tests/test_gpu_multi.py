@@ -31,9 +31,14 @@ needs_two = pytest.mark.skipif(_gpus() < 2, reason="needs at least two GPUs")
 @pytest.mark.parametrize("flags", [(), ("--no-multicast",)], ids=["multimem", "peer"])
 def test_collectives_are_exact_and_repeat_bit_for_bit(flags):
     rows = _run("collectives", "--gpus", str(_gpus()), "--min-kib", "1", "--max-mib", "4", "--repeats", "5", "--windows", "2", *flags)
-    validation = [row for row in rows if row[0] == "validation"][0]
-    assert int(validation[1]) == _gpus()
-    assert (int(validation[3]), int(validation[4]), int(validation[6])) == (0, 0, 0)
+    path = "peer" if flags else "multimem"
+    for name in ("validation", "validation_one_round"):  # the two-round form at the largest size, the one-round form at 64 KiB
+        validation = [row for row in rows if row[0] == name][0]
+        assert int(validation[1]) == _gpus()
+        assert (int(validation[3]), int(validation[4]), int(validation[6])) == (0, 0, 0)
+        assert validation[7] == path  # the kernels that ran are the ones the row claims
+    assert all(row[7] == path for row in rows if row[0] in ("all_reduce", "all_reduce_two_round", "reduce_scatter"))
+    assert any(row[0] == "all_reduce_two_round" for row in rows)
     assert any(row[0] == "barrier" for row in rows) and any(row[0] == "all_reduce" for row in rows)
     assert all(float(row[3]) > 0 for row in rows if row[0] in ("all_reduce", "reduce_scatter"))
 
