@@ -223,13 +223,14 @@ def _box_engine(context: RankContext):
 
 
 def _roofline_columns(rows: int, world: int, hidden: int, min_ms: float) -> str:
-    """``roofline_ms,fraction,source``: the step's bound (tensor time at the measured peak, or peer pulls at link
-    bandwidth, whichever is slower) and how much of it the measured time reaches."""
+    """``roofline_ms,fraction,source``: the step's bound (tensor time at the measured sustained peak, which is the one
+    that applies to steps timed in a long run, or peer pulls at link bandwidth, whichever is slower) and how much of it
+    the measured time reaches. The source names the denominator: ``measured-sustained`` or ``fallback-sustained``."""
     from .utils.roofline import load_peaks, loss_step_roofline_ms
 
     peaks = load_peaks()
-    bound = loss_step_roofline_ms(rows, world, hidden, peaks)
-    return f"{bound:.4f},{bound / min_ms:.3f},{peaks.source}"
+    bound = loss_step_roofline_ms(rows, world, hidden, peaks, sustained=True)
+    return f"{bound:.4f},{bound / min_ms:.3f},{peaks.source}-sustained"
 
 
 def _time(context: RankContext, step, windows: int, calls: int):

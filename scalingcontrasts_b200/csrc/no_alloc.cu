@@ -65,6 +65,16 @@ extern "C" int sc_fold_gradient_no_alloc(const void* cube, const void* candidate
         return fail(SC_NO_ALLOC_BAD_ARGUMENT,
                     "rows_q must be a multiple of 128, rows_c of 64, hidden of 16 and equal to the last prefix end", error,
                     error_capacity);
+    // The whole ladder is checked before anything is launched: ends are multiples of 16, strictly ascending, and cut the
+    // channels into at most 32 tiles of up to 256 channels (what one backward launch holds).
+    uint32_t begin = 0, tiles = 0;
+    for (uint32_t band = 0; band < prefixes; ++band) {
+        if (ends[band] % 16 || ends[band] <= begin)
+            return fail(SC_NO_ALLOC_BAD_ARGUMENT, "prefix ends must ascend strictly in multiples of 16", error, error_capacity);
+        tiles += (ends[band] - begin + 255) / 256;
+        begin = ends[band];
+    }
+    if (tiles > 32) return fail(SC_NO_ALLOC_BAD_ARGUMENT, "the ladder cuts the channels into more than 32 tiles", error, error_capacity);
     unsigned long long const needed = 2ull * rows_c * hidden;
     if (needed > SC_NO_ALLOC_WORKSPACE_BYTES) {
         char message[200];

@@ -16,15 +16,18 @@
 //   * Limit: rows_c * hidden * 2 bytes must not exceed SC_NO_ALLOC_WORKSPACE_BYTES (for example 1024 candidates of
 //     1024 channels, or 2048 of 512). Larger problems are refused with SC_NO_ALLOC_TOO_LARGE and a message; use the
 //     ordinary path for them.
-//   * The first call on each device looks up the array's device address (with that device current). Make that first
-//     call outside of any stream capture.
+//   * The first call on each device looks up the array's device address (with that device current) and keeps it. Make
+//     that first call outside of any stream capture. The kept address belongs to the device's current context: after a
+//     cudaDeviceReset() it is stale, and this entry point must not be called again in that process.
 //   * All calls on a device share the one workspace, and it keeps whatever the previous call left there. Nothing in it
 //     has to start at zero: each call overwrites the part it reads before reading it. Two calls whose kernels can run
 //     at the same time on one GPU (different streams, no ordering between them) race on the workspace; order them.
 //   * Inputs and outputs are the caller's: `cube` is [prefixes, rows_q, rows_c] bfloat16, `candidates` is
-//     [rows_c, hidden] bfloat16, `query_gradient` is [rows_q, hidden] float32 and is accumulated into. Pointers must be
-//     16-byte aligned device pointers on the current device; rows_q a multiple of 128, rows_c of 64, every end of 16,
-//     the last end equal to hidden. `status` may be null; when given it is the eight-word status block of the tile
+//     [rows_c, hidden] bfloat16, `query_gradient` is [rows_q, hidden] float32 and is accumulated into. These three must
+//     be 16-byte aligned device pointers on the current device. `ends` is a HOST array of `prefixes` values (it is read
+//     on the host, before anything is launched): strictly ascending multiples of 16, the last equal to hidden, cutting
+//     the channels into at most 32 tiles of up to 256. rows_q must be a multiple of 128, rows_c of 64. Anything else is
+//     refused with SC_NO_ALLOC_BAD_ARGUMENT before any kernel runs or the workspace is touched. `status` may be null; when given it is the eight-word status block of the tile
 //     kernels (a bounded wait that runs out is recorded there). `stream` is a cudaStream_t.
 //   * Returns SC_NO_ALLOC_OK, or an error code with a zero-terminated message in `error` (when `error` is not null).
 #pragma once

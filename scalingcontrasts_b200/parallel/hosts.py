@@ -3,8 +3,9 @@ blocks, then every GPU also scores the blocks that landed on its box.
 
 One step on a rank (host ``h``, local GPU ``g`` of ``G``), in the reference's order:
 
-1. drain: the rank's stream is synchronised and the box's ranks meet on the host, so that last step's readers of the
-   landing buffers are done and this step's parity buffer is free;
+1. no drain is needed: the landing buffer of this step's parity was last read by the remote rank two steps ago, and
+   that rank's post of the step in between, whose completion this rank consumed then, ran on the remote stream after
+   those reads (the reference synchronises its devices here because it has no such ordering to lean on);
 2. the block is published into the box's symmetric memory and posted on every rail (to GPU ``g`` of every other host)
    into the landing buffer of this step's parity; the writes fly while
 3. the rank scores the box's own blocks (the box step);
@@ -13,7 +14,8 @@ One step on a rank (host ``h``, local GPU ``g`` of ``G``), in the reference's or
 5. the rank scores every landed block of every remote host, pulling its peers' landed blocks over NVLink;
 6. ``finish``, and the summands are all-reduced inside the box;
 7. the box's sum crosses the rails as one row per host (GPU 0's rails); every host adds the rows in host order, so all
-   hosts hold bit-identical totals, and the totals are spread to the box's GPUs.
+   hosts hold bit-identical totals, and the totals are spread to the box's GPUs. Only GPU 0 of a box waits on the host
+   for this (an event on its stream, not a device-wide synchronise); the others enqueue the closing all-reduce and go on.
 
 With the loopback transport the "hosts" are groups of GPUs of one box. Parity: ``step_hosts`` (scalingcontrasts.cu:313-368),
 ``make_cluster`` (scalingcontrasts.cu:260-292).
@@ -31,6 +33,14 @@ from ..ladder import Matryoshka
 from ..ops.streamed_loss import BlockNorms, compute_block_norms
 from .box import BoxLoss, SourceBlock
 from .rail import RdmaRail, exchange_endpoint
+
+
+class _null_context:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *arguments):
+        return False
 
 
 class HostsLoss(BoxLoss):
@@ -60,6 +70,8 @@ class HostsLoss(BoxLoss):
             self.rails.append(rail)
         self.steps = 0
         self._host_summands = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32).pin_memory()
+        self._host_total = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32).pin_memory()
+        self._summands_ready = torch.cuda.Event()
 
     @staticmethod
     def heap_bytes_for(rows: int, hidden: int, prefixes: int, hosts: int) -> int:
@@ -67,14 +79,13 @@ class HostsLoss(BoxLoss):
         return BoxLoss.heap_bytes(rows, hidden, prefixes) + 2 * (hosts - 1) * per_block + 4096
 
     def step(self, queries: torch.Tensor, beta: float = 10.0, bias: float = -10.0, scalars: Optional[torch.Tensor] = None,
-             gradient_out: Optional[torch.Tensor] = None, stream=None, reduce: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+             gradient_out: Optional[torch.Tensor] = None, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One step across the hosts; the summands on return are always the world's sums (there is no unreduced form:
+        the closing all-reduce is also what spreads the hosts' totals inside the box)."""
         members, member, rows, hosts = self.members, self.member, self.rows, self.hosts
         parity = self.steps % 2
         world_rows = hosts * members * rows
         rank_base = (self.host * members + member) * rows
-        # 1. drain
-        torch.cuda.synchronize(self.device)
-        self.domain.host_barrier("hosts-drain")
         # 2. publish and post
         compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
         for rail in self.rails:
@@ -114,24 +125,28 @@ class HostsLoss(BoxLoss):
         self.loss.finish(self.embeddings, gradient, self.summands, stream)
         self.domain.all_reduce(SUMMAND_SLOTS, stream)
         # 7. hosts' sums in host order
-        self._host_summands.copy_(self.summands, non_blocking=False)
-        torch.cuda.synchronize(self.device)
         if member == 0:
-            row = [float(v) for v in self._host_summands.tolist()]
+            current = torch.cuda.current_stream(self.device) if stream is None else stream
+            with torch.cuda.stream(current):
+                self._host_summands.copy_(self.summands, non_blocking=True)
+                self._summands_ready.record(current)
+            self._summands_ready.synchronize()
             for rail in self.rails:
-                rail.post_summands(self.host, row)
+                rail.post_summands(self.host, self._host_summands.tolist())
             for rail in self.rails:
                 rail.await_landed(self.rail_timeout_s)
-            total = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32)
-            for host in range(hosts):
+            self._host_total.zero_()
+            for host in range(hosts):  # host order on every host: bit-identical totals everywhere
                 if host == self.host:
-                    total += self._host_summands
+                    self._host_total += self._host_summands
                 else:
                     rail = self.rails[self.remote_hosts.index(host)]
-                    total += torch.tensor(rail.read_summands(host, SUMMAND_SLOTS), dtype=torch.float32)
-            self.summands.copy_(total)
+                    self._host_total += torch.tensor(rail.read_summands(host, SUMMAND_SLOTS), dtype=torch.float32)
+            with torch.cuda.stream(current):
+                self.summands.copy_(self._host_total, non_blocking=True)
         else:
-            self.summands.zero_()
+            with torch.cuda.stream(stream) if stream is not None else _null_context():
+                self.summands.zero_()
         self.domain.all_reduce(SUMMAND_SLOTS, stream)
         self.steps += 1
         return gradient, self.summands

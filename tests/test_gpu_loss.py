@@ -206,3 +206,113 @@ def test_scratch_does_not_grow_and_device_scalars_override():
     torch.cuda.synchronize()
     assert loss.bytes() == before
     assert torch.equal(outputs[0][0], outputs[1][0]) and torch.equal(outputs[0][1], outputs[1][1])
+
+
+@pytest.mark.parametrize("beta,bias", [(5.0, 0.0), (20.0, -3.0), (1.0, 2.0)])
+@pytest.mark.parametrize("spec", [LossSpec("self"), LossSpec("pairs")], ids=lambda s: s.positives)
+@pytest.mark.parametrize("through_device", [False, True], ids=["host-scalars", "device-scalars"])
+def test_learned_scale_and_bias_against_the_float64_oracle(beta, bias, spec, through_device):
+    """Away from beta = 10, bias = -10 most cells leave the easy-negative series path: logits near and above zero take
+    the general form (decay of the absolute value, reciprocal, full log1p polynomial, hinge), and a warp's patch may mix
+    both. Checked against the float64 evaluation with the scalars given as host floats and through the device pointer a
+    trainer uses."""
+    rows, hidden, prefixes = 256, 256, 3
+    ladder = Matryoshka.halvings(hidden, prefixes)
+    blocks = [normal_embeddings(rows, hidden, seed=3, rank=r).cuda() for r in range(2)]
+    expected = oracle(torch.cat(blocks).cpu(), ladder, beta, bias, spec)
+    loss = _loss(rows, hidden, ladder, spec)
+    scalars = torch.tensor([beta, bias], device="cuda") if through_device else None
+    total = torch.zeros(12, dtype=torch.float64)
+    gradients = []
+    for rank in range(2):
+        loss.begin(blocks[rank])
+        for peer in (rank, 1 - rank):
+            loss.score(blocks[rank], blocks[peer], rank * rows, peer * rows, 0.0 if through_device else beta,
+                       0.0 if through_device else bias, 2 * rows, scalars=scalars)
+        gradient, summands = loss.finish(blocks[rank])
+        torch.cuda.synchronize()
+        loss.check()
+        gradients.append(gradient.float().cpu())
+        total += summands.double().cpu()
+    assert float(total[0]) == pytest.approx(expected.loss, rel=2e-6)
+    assert torch.allclose(total[4:4 + prefixes], expected.band_losses, rtol=2e-6)
+    assert relative_l2(torch.cat(gradients), expected.gradient) < 4e-3
+    assert float(total[1]) == pytest.approx(expected.bias_grad, rel=1e-4)
+    assert float(total[2]) == pytest.approx(expected.log_beta_grad, rel=1e-3, abs=1e-6)
+
+
+def test_pull_inside_the_forward_launch_copies_the_bytes_and_changes_nothing():
+    """``simulate`` with ``pull=True`` scores blocks 1.. from the staging buffers that the forward launch of the block
+    before filled with its pull warp; with ``pull=False`` every block is scored from the source. Same bits either way,
+    and the staged bytes (embeddings and norms) equal the source."""
+    from scalingcontrasts_b200.parallel.box import BoxLoss
+
+    rows, hidden = 512, 768
+    ladder = Matryoshka.halvings(hidden, 5)
+    engine = BoxLoss(rows, hidden, ladder, LossSpec("pairs"), None, "cuda")
+    block = normal_embeddings(rows, hidden, seed=9, rank=0).cuda()
+    outcomes = []
+    for pull in (True, False):
+        for staged in engine.staged:
+            staged.zero_()
+        gradient, summands = engine.simulate(block, 4, pull=pull)
+        torch.cuda.synchronize()
+        engine.check()
+        outcomes.append((gradient.clone(), summands.clone()))
+        if pull:
+            for slot in range(2):
+                assert torch.equal(engine.staged[slot], block)
+                assert torch.equal(engine.staged_norms[slot].storage, engine.norms.storage)
+    assert torch.equal(outcomes[0][0], outcomes[1][0]) and torch.equal(outcomes[0][1], outcomes[1][1])
+
+
+def test_backward_split_over_candidates_matches_the_single_pass():
+    """``backward_split`` divides the candidate range between CTAs that add with float32 reductions in no fixed order:
+    the same gradient as the single pass to float32 rounding (and the summands, which do not pass through it, to the bit)."""
+    from scalingcontrasts_b200.ops.streamed_loss import StreamedLoss
+
+    rows, hidden = 512, 256
+    ladder = Matryoshka.halvings(hidden, 3)
+    queries = normal_embeddings(rows, hidden, seed=13, rank=0).cuda()
+    outcomes = []
+    for split in (1, 4):
+        loss = StreamedLoss(rows, hidden, ladder, LossSpec("self"), "cuda", backward_split=split, fused=False)
+        loss.begin(queries)
+        loss.score(queries, queries, 0, 0, 10.0, -10.0, rows)
+        torch.cuda.synchronize()
+        loss.check()
+        outcomes.append((loss.query_gradient.clone(), loss.row_accumulators.clone()))
+    assert relative_l2(outcomes[1][0], outcomes[0][0]) < 1e-5
+    assert torch.equal(outcomes[0][1], outcomes[1][1])
+
+
+@pytest.mark.parametrize("fused", [False, True], ids=["two-kernel", "fused"])
+def test_twenty_repeats_of_a_many_tile_step_and_poisoned_scratch(fused):
+    """4096 rows against themselves, the real ladder, twenty times: every CTA walks many tiles and the rings wrap, and
+    every repeat must reproduce the first one's loss summands bit for bit (per-row sums are folded in a fixed order). The
+    two-kernel form also reproduces the gradient bit for bit; the fused form adds one partial gradient per run of tiles
+    with float32 reductions whose order is not fixed, so its gradient repeats to rounding only. Before every repeat the
+    scratch buffers are filled with NaN bit patterns: nothing may be read before it is written."""
+    rows, hidden = 4096, 768
+    ladder = Matryoshka.halvings(hidden, 5)
+    queries = normal_embeddings(rows, hidden, seed=21, rank=0).cuda()
+    loss = _loss(rows, hidden, ladder, LossSpec("pairs"), fused=fused)
+    first = None
+    for repeat in range(20):
+        for scratch in (loss.partials, loss.similarity_gradients, loss.transposed_candidates, loss.candidate_norms.storage,
+                        loss.query_gradient, loss.row_accumulators):
+            scratch.view(torch.int16 if scratch.dtype == torch.bfloat16 else torch.int32).fill_(-1)  # all ones: a NaN
+        loss.begin(queries)
+        loss.score(queries, queries, 0, 0, 10.0, -10.0, rows)
+        gradient, summands = loss.finish(queries)
+        torch.cuda.synchronize()
+        loss.check()
+        assert bool(torch.isfinite(summands).all()) and bool(torch.isfinite(gradient.float()).all())
+        if first is None:
+            first = (gradient.clone(), summands.clone())
+            continue
+        assert torch.equal(summands, first[1]), f"repeat {repeat}: the loss summands changed bits"
+        if fused:
+            assert relative_l2(gradient.float(), first[0].float()) < 1e-3
+        else:
+            assert torch.equal(gradient, first[0]), f"repeat {repeat}: the gradient changed bits"

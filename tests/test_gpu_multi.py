@@ -75,6 +75,17 @@ def test_gradient_reducer_matches_nccl_sum():
 
 
 @needs_two
+def test_box_steps_without_the_closing_all_reduce_and_as_cuda_graphs():
+    script = os.path.join(ROOT, "tests", "multi_box_check.py")
+    environment = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    result = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={min(_gpus(), 4)}",
+                             "--master-addr", "127.0.0.1", "--master-port", "29633", script], cwd=ROOT, env=environment,
+                            capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stdout[-3000:] + result.stderr[-3000:]
+    assert "box steps ok" in result.stdout
+
+
+@needs_two
 def test_hosts_mode_over_loopback_rails_against_float64():
     """Two logical hosts on this box, their blocks crossing the rails, checked like the box oracle."""
     gpus = _gpus() - _gpus() % 2

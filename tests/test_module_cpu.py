@@ -37,11 +37,23 @@ def test_state_dict_keeps_the_siglip_layout_and_initial_values():
     assert float(other.logit_bias) == -10.0
 
 
-def test_roofline_columns_use_the_measured_file_or_say_fallback():
-    from scalingcontrasts_b200.utils.roofline import load_peaks, loss_step_roofline_ms
+def test_roofline_columns_use_the_measured_file_or_say_fallback(tmp_path, monkeypatch):
+    import json
 
+    from scalingcontrasts_b200.utils.roofline import FALLBACK_BF16_TFLOPS, load_peaks, loss_step_roofline_ms
+
+    # no file named, none in the working directory: the fallback figures, labelled as such
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.delenv("SC_MEASURED_PEAKS", raising=False)
+    fallback = load_peaks()
+    assert fallback.source == "fallback" and fallback.bf16_tflops == FALLBACK_BF16_TFLOPS
+    # a file named by the environment variable, or explicitly
+    path = tmp_path / "peaks.json"
+    path.write_text(json.dumps({"hbm_gbs": 6000.0, "bf16_tflops": 1600.0, "bf16_tflops_sustained": 1400.0}))
+    monkeypatch.setenv("SC_MEASURED_PEAKS", str(path))
     peaks = load_peaks()
-    assert peaks.source in ("measured", "fallback") and peaks.bf16_tflops > 0
-    # R = 16384, 8 GPUs, H = 768: 9.69 TFLOP of tensor work per rank
-    bound = loss_step_roofline_ms(16384, 8, 768, peaks)
-    assert abs(bound - 2.0 * 1536 * 16384 * 131072 / (peaks.bf16_tflops * 1e12) * 1e3) < 1e-9
+    assert peaks.source == "measured" and peaks.bf16_tflops == 1600.0 and load_peaks(str(path)) == peaks
+    # R = 16384, 8 GPUs, H = 768: 9.69 TFLOP of tensor work per rank; a step row uses the sustained peak, a kernel row the burst
+    flops = 2.0 * 1536 * 16384 * 131072
+    assert abs(loss_step_roofline_ms(16384, 8, 768, peaks) - flops / (1400.0 * 1e12) * 1e3) < 1e-9
+    assert abs(loss_step_roofline_ms(16384, 8, 768, peaks, sustained=False) - flops / (1600.0 * 1e12) * 1e3) < 1e-9

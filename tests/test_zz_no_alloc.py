@@ -72,5 +72,12 @@ def test_sizes_beyond_the_workspace_and_bad_shapes_are_refused(ext):
     small = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     code, message = _call(function, cube, small, torch.zeros(100, 64, device="cuda"), [64], 1.0, status)
     assert code == 2 and "multiple of 128" in message
+    # ladders that do not ascend, or whose ends are not multiples of 16, are refused before anything is launched
+    candidates = torch.zeros(64, 256, dtype=torch.bfloat16, device="cuda")
+    cube = torch.zeros(3, 128, 64, dtype=torch.bfloat16, device="cuda")
+    gradient_small = torch.zeros(128, 256, device="cuda")
+    for ends in ([128, 64, 256], [64, 64, 256], [24, 128, 256]):
+        code, message = _call(function, cube, candidates, gradient_small, ends, 1.0, status)
+        assert code == 2 and "ascend" in message, (ends, code, message)
     torch.cuda.synchronize()
-    assert int(gradient.abs().sum()) == 0  # a refused call touches nothing
+    assert int(gradient.abs().sum()) == 0 and int(gradient_small.abs().sum()) == 0  # a refused call touches nothing
