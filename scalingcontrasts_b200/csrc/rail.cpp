@@ -190,6 +190,11 @@ void loopback_rail::post_summands(int row, float const* values, int count) {
     if (!connected_) throw std::runtime_error("rail: post before connect");
     if (row < 0 || row >= hosts_) throw std::runtime_error("rail: bad summands row");
     if (count < 1 || count > rail_summand_floats) throw std::runtime_error("rail: a summands row holds 1..16 floats");
+    // A reliable connection delivers its writes in the order they were posted. The embeddings' completion is pushed by a
+    // host callback on the rail's stream, this one by the calling thread: wait for the stream, so that a completion
+    // posted earlier can never arrive after this one (the caller need not have synchronised the device).
+    check(cudaSetDevice(device_), "cudaSetDevice");
+    check(cudaStreamSynchronize(stream_), "ordering a summands row after the embeddings posted before it");
     for (int i = 0; i < count; ++i) remote_mailbox_->summands[row][i] = values[i];
     std::atomic_thread_fence(std::memory_order_release);
     uint32_t const status = injected_status_;
