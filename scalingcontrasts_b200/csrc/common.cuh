@@ -153,6 +153,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, wait_co
     return mbar_wait_timed(bar, parity, ctx.status, ctx.budget_ns, ctx.abort_flag, site, detail);
 }
 
+// The same wait for a helper warp that shares its scheduler with warps doing arithmetic: between attempts it sleeps, so
+// that its polling does not take issue slots from them. The price is up to `sleep_ns` of wake-up latency, which suits
+// waits that have slack (a producer ahead of its consumer) and not those on a critical path.
+static __device__ __noinline__ bool mbar_wait_sleeping(uint32_t bar, uint32_t parity, uint32_t* status, uint64_t budget_ns,
+                                                       uint32_t volatile* abort_flag, uint32_t site, uint32_t detail,
+                                                       uint32_t sleep_ns) {
+    uint64_t const start = global_timer_ns();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 64; ++spin) {
+            __nanosleep(sleep_ns);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag != 0u) return false;
+        if (global_timer_ns() - start > budget_ns) {
+            record_failure(status, status_timeout_pipeline, site, detail, parity, bar);
+            *abort_flag = 1u;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
+                                                  uint32_t detail, uint32_t sleep_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_sleeping(bar, parity, ctx.status, ctx.budget_ns, ctx.abort_flag, site, detail, sleep_ns);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor loads into this CTA's shared memory, completion counted on an mbarrier. No load in this
 // library carries a cluster multicast qualifier, and no tensor map covers another GPU's memory.

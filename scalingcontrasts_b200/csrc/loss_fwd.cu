@@ -263,10 +263,20 @@ __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::
 // values the compiler can keep in uniform registers, which is where those instructions take their operands from. (Run
 // by a single lane inside a divergent branch, every operand would cross from a vector to a uniform register first.)
 // Every lane waits; the answer is the same in every lane.
+// Their waits sleep between attempts (`sleep_ns`; 0 polls back to back): a helper warp shares its scheduler with four
+// epilogue warps, and a warp that polls an mbarrier without pause issues about as many instructions as one of them.
+#ifndef SC_FWD_HELPER_SLEEP
+#define SC_FWD_HELPER_SLEEP 1
+#endif
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, wait_context const& ctx, uint32_t site,
-                                               uint32_t detail) {
+                                               uint32_t detail, uint32_t sleep_ns = 0) {
+    if (SC_FWD_HELPER_SLEEP && sleep_ns != 0u)
+        return __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(bar, parity, ctx, site, detail, sleep_ns));
     return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, ctx, site, detail));
 }
+constexpr uint32_t sleep_producer_ns = 1000; // stages ahead of the issuer: nothing waits for this warp's wake-up
+constexpr uint32_t sleep_issuer_ns = 100;    // the epilogue may be waiting for the tile these UMMAs finish
+constexpr uint32_t sleep_gemm_ns = 500;      // the fused kernel's gradient GEMM runs a whole item behind
 
 __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensorMap const* c_map, fwd_params const& p,
                                               uint32_t stages_base, fwd_tail* tail, wait_context const& ctx,
@@ -282,7 +292,8 @@ __device__ __forceinline__ void producer_role(CUtensorMap const* q_map, CUtensor
             uint32_t const column_tile = run * p.tiles_per_run + t;
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
                 timer.lap(0);
-                if (!mbar_wait_warp(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_fwd_stage_empty, item, sleep_producer_ns))
+                    return;
                 timer.lap(1);
                 uint32_t const full = smem_u32(&tail->stage_full[stage]);
                 uint32_t const destination = stages_base + stage * fwd_stage_bytes;
@@ -318,7 +329,8 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
             for (int chunk = static_cast<int>(chunks) - 1; chunk >= 0; --chunk) {
                 uint32_t const starts = p.band_starts[chunk];
                 timer.lap(0);
-                if (!mbar_wait_warp(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->stage_full[stage]), phase, ctx, site_fwd_stage_full, tile_local, sleep_issuer_ns))
+                    return;
                 timer.lap(1);
                 tcgen05_fence_after();
                 uint32_t const low = low_base + stage * (fwd_stage_bytes >> 4);
@@ -336,14 +348,14 @@ __device__ __forceinline__ void mma_role(fwd_params const& p, uint32_t stages_ba
                             if (rank < 2) {
                                 while (seen_early <= needed) {
                                     if (!mbar_wait_warp(smem_u32(&tail->tile_early[seen_early % fwd_slots]),
-                                                        (seen_early / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit))
+                                                        (seen_early / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit, sleep_issuer_ns))
                                         return;
                                     ++seen_early;
                                 }
                             } else {
                                 while (seen_late <= needed) {
                                     if (!mbar_wait_warp(smem_u32(&tail->tile_late[seen_late % fwd_slots]),
-                                                        (seen_late / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit))
+                                                        (seen_late / fwd_slots) & 1u, ctx, site_fwd_slot_empty, unit, sleep_issuer_ns))
                                         return;
                                     ++seen_late;
                                 }
@@ -833,7 +845,8 @@ __device__ __forceinline__ void fz_producer_role(fz_maps const* maps, fwd_params
     for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x, ++local) {
         uint32_t const buffer = local & 1u;
         timer.lap(0);
-        if (!mbar_wait_warp(smem_u32(&tail->fz_item_stored[buffer]), (local >> 1) & 1u, ctx, site_fz_item_stored, item)) return;
+        if (!mbar_wait_warp(smem_u32(&tail->fz_item_stored[buffer]), (local >> 1) & 1u, ctx, site_fz_item_stored, item, sleep_producer_ns))
+            return;
         timer.lap(1);
         fence_proxy_async_all();
         uint32_t const first_candidate = (item % p.runs_per_strip) * p.tiles_per_run * fwd_cols;
@@ -842,7 +855,8 @@ __device__ __forceinline__ void fz_producer_role(fz_maps const* maps, fwd_params
             uint32_t const band = word & 0xFu, channel0 = ((word >> 4) & 0xFFFu) * 16u, width = (word >> 16) * 16u;
             for (uint32_t block = 0; block < p.tiles_per_run; ++block) {
                 timer.lap(0);
-                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_empty[stage]), phase ^ 1u, ctx, site_fz_stage_empty, which)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_empty[stage]), phase ^ 1u, ctx, site_fz_stage_empty, which, sleep_gemm_ns))
+                    return;
                 timer.lap(2);
                 uint32_t const full = smem_u32(&tail->fz_stage_full[stage]);
                 uint32_t const destination = stages_base + stage * fz_stage_bytes;
@@ -885,12 +899,12 @@ __device__ __forceinline__ void fz_mma_role(fwd_params const& p, uint32_t stages
             // The accumulator's previous contents must have left tensor memory (an arrival per epilogue warp).
             timer.lap(0);
             if (unit != 0 &&
-                !mbar_wait_warp(smem_u32(&tail->fz_accumulator_empty), (unit - 1) & 1u, ctx, site_fz_accumulator_empty, unit))
+                !mbar_wait_warp(smem_u32(&tail->fz_accumulator_empty), (unit - 1) & 1u, ctx, site_fz_accumulator_empty, unit, sleep_gemm_ns))
                 return;
             timer.lap(1);
             tcgen05_fence_after();
             for (uint32_t block = 0; block < p.tiles_per_run; ++block) {
-                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_full[stage]), phase, ctx, site_fz_stage_full, unit)) return;
+                if (!mbar_wait_warp(smem_u32(&tail->fz_stage_full[stage]), phase, ctx, site_fz_stage_full, unit, sleep_gemm_ns)) return;
                 timer.lap(2);
                 tcgen05_fence_after();
                 uint32_t const a_low = low_base + stage * (fz_stage_bytes >> 4);

@@ -27,6 +27,7 @@ import torch
 from ..config import LossSpec, REFERENCE_SPEC, SUMMAND_SLOTS
 from ..ladder import Matryoshka
 from ..ops.streamed_loss import BlockNorms, PullRequest, StreamedLoss, compute_block_norms
+from ..utils.trace import phase
 
 
 def _check_gradient(gradient: torch.Tensor, rows: int, hidden: int) -> None:
@@ -116,8 +117,9 @@ class BoxLoss:
                 candidates, norms = self.staged[slot], self.staged_norms[slot]
             following = blocks[index + 1] if index + 1 < len(blocks) else None
             pull = self._pull(following, index % 2) if following is not None and not following.local else None
-            self.loss.score(self.embeddings, candidates, query_base, block.candidate_base, beta, bias, live, stream,
-                            candidate_norms=norms, scalars=scalars, pull_next=pull)
+            with phase(f"score block at {block.candidate_base}" + (" + pull of the next" if pull is not None else "")):
+                self.loss.score(self.embeddings, candidates, query_base, block.candidate_base, beta, bias, live, stream,
+                                candidate_norms=norms, scalars=scalars, pull_next=pull)
 
     # ------------------------------------------------------------------------------------------------------
     def _core(self, beta: float, bias: float, scalars: Optional[torch.Tensor], gradient: torch.Tensor, reduce: bool,
@@ -126,7 +128,8 @@ class BoxLoss:
         ``scalars`` and ``gradient``, which is what makes it replayable as a CUDA graph."""
         members, member, rows = self.members, self.member, self.rows
         if self.domain is not None:
-            self.domain.barrier(stream)
+            with phase("barrier: every block is published"):
+                self.domain.barrier(stream)
         self.loss.begin(self.embeddings, stream, query_norms=self.norms)
         blocks: List[SourceBlock] = [SourceBlock(member * rows, self.embeddings, self.norms)]
         for p in range(1, members):
@@ -134,7 +137,8 @@ class BoxLoss:
             blocks.append(SourceBlock(peer * rows, member=peer, embeddings_offset=self._embeddings_offset,
                                       norms_offset=self._norms_offset))
         self.score_sequence(blocks, member * rows, members * rows, beta, bias, scalars, stream)
-        self.loss.finish(self.embeddings, gradient, self.summands, stream)
+        with phase("finish: self term, cast, summands"):
+            self.loss.finish(self.embeddings, gradient, self.summands, stream)
         if self.domain is not None:
             # Either collective closes the step: its rounds are also the fence that says "every peer has finished
             # reading my block", without which the next step's publish could overwrite a block still being pulled.
@@ -154,7 +158,8 @@ class BoxLoss:
         argument set as a CUDA graph and replayed afterwards, so a step costs the host two launches however many
         blocks it scores; the first call of an argument set runs eagerly, the second captures. Every member of the
         domain must make the same choice in the same step."""
-        compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
+        with phase("publish: prefix norms + copy into symmetric memory"):
+            compute_block_norms(queries, self.ladder, self.norms, copy_to=self.embeddings, stream=stream)
         gradient = self.gradient if gradient_out is None else gradient_out
         _check_gradient(gradient, self.rows, self.hidden)
         if (self.use_graphs if graph is None else graph) and stream is None:

@@ -21,6 +21,7 @@ from .ladder import Matryoshka
 from .models.loss import MatryoshkaSigmoidLoss
 from .models.projector import Projector
 from .parallel.reducer import GradientReducer
+from .utils.trace import phase
 
 
 class ContrastiveTrainer:
@@ -107,11 +108,15 @@ class ContrastiveTrainer:
     def step_on_device(self, x: torch.Tensor) -> torch.Tensor:
         """One step on a batch that already lives on the device; returns the loss as a device scalar."""
         self.optimizer.zero_grad(set_to_none=True)
-        embeddings = self.projector(x)
-        loss = self.loss(embeddings)
-        loss.backward()
-        self.reducer.wait()
-        self.optimizer.step()
+        with phase("projector forward"):
+            embeddings = self.projector(x)
+        with phase("loss step"):
+            loss = self.loss(embeddings)
+        with phase("backward + overlapped gradient all-reduce"):
+            loss.backward()
+            self.reducer.wait()
+        with phase("optimizer"):
+            self.optimizer.step()
         self.steps_done += 1
         return loss
 

@@ -23,6 +23,10 @@ if os.environ.get("SC_FWD_EPILOGUE_WARPS"):
 if os.environ.get("SC_FWD_TRACE"):
     NVCC_FLAGS.append("-DSC_FWD_TRACE=" + os.environ["SC_FWD_TRACE"])
 
+# A/B switch for the helper warps' sleeping waits in the forward kernel (1: sleep between polls, 0: poll back to back).
+if os.environ.get("SC_FWD_HELPER_SLEEP"):
+    NVCC_FLAGS.append("-DSC_FWD_HELPER_SLEEP=" + os.environ["SC_FWD_HELPER_SLEEP"])
+
 setup(
     name="scalingcontrasts_b200",
     version="0.1.0",

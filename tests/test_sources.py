@@ -44,4 +44,9 @@ def test_every_device_wait_is_bounded():
     """No `while`/`for(;;)` spin in device code without a budget: the wait helpers are the only loops on flags."""
     common, collectives = _read("common.cuh"), _read("collectives.cu")
     assert "budget_ns" in common and "budget_ns" in collectives
-    assert common.count("for (;;)") == 1 and collectives.count("for (;;)") == 1
+    # the two mbarrier waits (polling back to back, and sleeping between polls) and the collectives' flag wait
+    assert common.count("for (;;)") == 2 and collectives.count("for (;;)") == 1
+    for text in (common, collectives):
+        for loop in re.finditer(r"for \(;;\) \{", text):
+            body = text[loop.end():loop.end() + 900]
+            assert "budget_ns" in body, "a spin loop without a budget"
