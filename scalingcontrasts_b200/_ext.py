@@ -23,7 +23,9 @@ def _try_import():
     try:
         import torch  # noqa: F401  (the extension links against torch's libraries)
 
-        _module = importlib.import_module("scalingcontrasts_b200._C")
+        # SC_NATIVE_VARIANT=bounds loads the bounds-checked debug build of the same sources instead
+        variant = os.environ.get("SC_NATIVE_VARIANT", "")
+        _module = importlib.import_module("scalingcontrasts_b200._C" + ("_" + variant if variant else ""))
     except BaseException as error:  # ImportError, or OSError from the dynamic loader
         _error = error
 

@@ -145,7 +145,8 @@ void launch_forward(forward_arguments const& arguments, cudaStream_t stream);
 
 struct backward_arguments {
     void const* gradient_cube_bf16;     // [K, rows_q, rows_c]
-    void const* transposed_candidates;  // [hidden, rows_c]
+    void const* transposed_candidates;  // [hidden, rows_c]; may be null when the row-major block is given
+    void const* candidates_row_major;   // [rows_c, hidden] as the block lies in memory; preferred when set (hidden >= 64)
     float* query_gradient;              // [rows_q, hidden], accumulated
     uint32_t* status;
     uint32_t rows_q, rows_c, hidden;
@@ -157,6 +158,16 @@ struct backward_arguments {
 void launch_backward(backward_arguments const& arguments, cudaStream_t stream);
 
 void preload_loss_kernels();
+
+// -------- bounds-checked debug build ----------------------------------------------------------------------------
+// True in the build with -DSC_BOUNDS=1, in which kernels compare every computed global index with its limit. The
+// readers copy out the first recorded miss of each translation unit (eight words, all zero when there was none; always
+// zero in the ordinary build).
+bool bounds_build();
+void bounds_record_small(uint32_t* out);
+void bounds_record_forward(uint32_t* out);
+void bounds_record_backward(uint32_t* out);
+void bounds_record_collectives(uint32_t* out);
 
 // -------- oracle twin (oracle_cpu.cpp) ---------------------------------------------------------------------------
 // Plain triple loop in float64; gradient [n, hidden]; out[0]=loss, out[1]=bias grad, out[2]=log-beta grad,

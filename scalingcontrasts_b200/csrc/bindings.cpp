@@ -82,12 +82,15 @@ struct loss_plan {
     uint64_t budget_ns = 0;
     int multiprocessors = 0;
 
+    bool transpose_candidates = true; // false: the backward kernel reads the block as it lies (MN-major operand)
+
     void score(uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t query_base,
                uint64_t candidate_base, float beta, float bias, double live, uint64_t scalars, uint64_t pull_src0,
                uint64_t pull_dst0, uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1,
                uint64_t stream_handle) const {
         cudaStream_t const stream = stream_of(stream_handle);
-        sc::launch_transpose(pointer<void>(candidates), pointer<void>(transposed), rows_c, hidden, stream);
+        bool const transposing = fused || transpose_candidates || hidden < 64;
+        if (transposing) sc::launch_transpose(pointer<void>(candidates), pointer<void>(transposed), rows_c, hidden, stream);
         sc::forward_arguments a{};
         a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
         a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
@@ -108,7 +111,9 @@ struct loss_plan {
         sc::launch_fold_partials(pointer<float>(partials), pointer<float>(accumulators), rows_q, partial_slots, quantities, stream);
         if (!fused) {
             sc::backward_arguments b{};
-            b.gradient_cube_bf16 = pointer<void>(gradients), b.transposed_candidates = pointer<void>(transposed);
+            b.gradient_cube_bf16 = pointer<void>(gradients);
+            b.transposed_candidates = transposing ? pointer<void>(transposed) : nullptr;
+            b.candidates_row_major = transposing ? nullptr : pointer<void>(candidates);
             b.query_gradient = pointer<float>(query_gradient), b.status = pointer<uint32_t>(status);
             b.rows_q = rows_q, b.rows_c = rows_c, b.hidden = hidden, b.ladder = ladder, b.split = backward_split;
             b.scale = static_cast<float>(2.0 / live), b.budget_ns = budget_ns;
@@ -252,7 +257,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("partial_slots"), py::arg("quantities"), py::arg("backward_split"), py::arg("spec_code"), py::arg("fused"),
              py::arg("gradients"), py::arg("gradients_bytes"), py::arg("transposed"), py::arg("query_gradient"),
              py::arg("partials"), py::arg("accumulators"), py::arg("status"), py::arg("budget_ns"), py::arg("multiprocessors"))
+        .def_readwrite("transpose_candidates", &loss_plan::transpose_candidates)
         .def("score", &loss_plan::score);
+    m.attr("BOUNDS_BUILD") = sc::bounds_build();
+    m.def("bounds_records", []() {
+        // the first out-of-range index each translation unit recorded (all zeros: none); ordinary builds never record
+        std::vector<std::vector<uint32_t>> records(4, std::vector<uint32_t>(8, 0u));
+        sc::bounds_record_small(records[0].data());
+        sc::bounds_record_forward(records[1].data());
+        sc::bounds_record_backward(records[2].data());
+        sc::bounds_record_collectives(records[3].data());
+        return records;
+    });
     m.def("note_launches", [](uint64_t count) { sc::note_launch(count); });
     m.def("forward_partial_slots", &sc::forward_partial_slots);
     m.def("forward_quantities", &sc::forward_quantities);
@@ -298,14 +314,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("gradient_scale") = 0.0f);
     m.def("backward", [](uint64_t cube, uint64_t transposed, uint64_t query_gradient, uint64_t status, uint32_t rows_q,
                          uint32_t rows_c, uint32_t hidden, std::vector<uint32_t> const& ends, uint32_t split, float scale,
-                         uint64_t budget_ns, uint64_t stream) {
+                         uint64_t budget_ns, uint64_t stream, uint64_t row_major) {
         sc::backward_arguments a{};
         a.gradient_cube_bf16 = pointer<void>(cube), a.transposed_candidates = pointer<void>(transposed);
+        a.candidates_row_major = pointer<void>(row_major);
         a.query_gradient = pointer<float>(query_gradient), a.status = pointer<uint32_t>(status);
         a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder_of(ends), a.split = split, a.scale = scale;
         a.budget_ns = budget_ns;
         sc::launch_backward(a, stream_of(stream));
-    });
+    }, py::arg("cube"), py::arg("transposed"), py::arg("query_gradient"), py::arg("status"), py::arg("rows_q"), py::arg("rows_c"),
+       py::arg("hidden"), py::arg("ends"), py::arg("split"), py::arg("scale"), py::arg("budget_ns"), py::arg("stream"),
+       py::arg("row_major") = 0);
 
     m.def("keyed_embeddings", [](uint64_t rows, uint32_t row_count, uint32_t hidden, uint64_t salt, float scale, uint64_t stream) {
         sc::launch_keyed_embeddings(pointer<void>(rows), row_count, hidden, salt, scale, stream_of(stream));

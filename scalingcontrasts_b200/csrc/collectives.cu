@@ -322,6 +322,7 @@ __global__ void __launch_bounds__(small_threads)
     uint32_t const parity = (round / c.members) & 1u;
     size_t const mine = static_cast<size_t>(parity * c.members + c.member) * slot_bytes;
     for (uint32_t v = threadIdx.x; v < vectors; v += blockDim.x) {
+        if (!SC_IN_BOUNDS(static_cast<size_t>(v) * 16 + 15, slot_bytes)) continue;
         vec4 const value = load_vec(own_payload + static_cast<size_t>(v) * 16);
         if constexpr (multicast_) {
             multimem_store<payload_type::f32>(slots + mine + static_cast<size_t>(v) * 16, value);
@@ -407,6 +408,7 @@ void launch_reduce_scatter_shape(shape_t shape, control_view const& control, cha
 } // namespace
 
 int last_collective_path() { return last_path.load(); }
+SC_DEFINE_BOUNDS_READER(bounds_record_collectives)
 
 void launch_barrier(control_view const& control, cudaStream_t stream) {
     barrier_kernel<<<1, 32, 0, stream>>>(control);

@@ -73,6 +73,44 @@ __device__ __forceinline__ bool status_poisoned(uint32_t const* status) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Bounds-checked debug build (-DSC_BOUNDS=1): every index into global memory that a kernel computes is compared with
+// its limit first. A miss is recorded (first one wins: code, source line, index, limit, block, thread) in a record that
+// the host reads, and the access is skipped; nothing traps. In the ordinary build the check compiles to `true`. The
+// record lives once per translation unit; SC_DEFINE_BOUNDS_READER gives the unit a host function that copies it out.
+// ---------------------------------------------------------------------------------------------------------------
+#ifndef SC_BOUNDS
+#define SC_BOUNDS 0
+#endif
+#if SC_BOUNDS
+static __device__ uint32_t bounds_record[8];
+__device__ __forceinline__ bool in_bounds(uint64_t index, uint64_t limit, uint32_t line) {
+    if (index < limit) return true;
+    if (atomicCAS(&bounds_record[0], 0u, static_cast<uint32_t>(status_bad_argument)) == 0u) {
+        bounds_record[1] = line;
+        bounds_record[2] = static_cast<uint32_t>(index), bounds_record[3] = static_cast<uint32_t>(index >> 32);
+        bounds_record[4] = static_cast<uint32_t>(limit), bounds_record[5] = static_cast<uint32_t>(limit >> 32);
+        bounds_record[6] = blockIdx.x, bounds_record[7] = threadIdx.x;
+    }
+    return false;
+}
+#define SC_IN_BOUNDS(index, limit) ::sc::in_bounds(static_cast<uint64_t>(index), static_cast<uint64_t>(limit), __LINE__)
+// The same for a whole converged warp in front of a warp-wide instruction: all lanes pass or all lanes skip.
+#define SC_WARP_IN_BOUNDS(index, limit) __all_sync(0xFFFFFFFFu, SC_IN_BOUNDS(index, limit))
+#define SC_DEFINE_BOUNDS_READER(name)                                                                                   \
+    void name(uint32_t* out) {                                                                                          \
+        if (cudaMemcpyFromSymbol(out, bounds_record, sizeof(bounds_record)) != cudaSuccess)                             \
+            for (int i = 0; i < 8; ++i) out[i] = 0xFFFFFFFFu;                                                           \
+    }
+#else
+#define SC_IN_BOUNDS(index, limit) true
+#define SC_WARP_IN_BOUNDS(index, limit) true
+#define SC_DEFINE_BOUNDS_READER(name)                                                                                   \
+    void name(uint32_t* out) {                                                                                          \
+        for (int i = 0; i < 8; ++i) out[i] = 0u;                                                                        \
+    }
+#endif
+
+// ---------------------------------------------------------------------------------------------------------------
 // Shared-memory addresses and mbarriers
 // ---------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(void const* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -261,6 +299,9 @@ __device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addres
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
+
+// Bit that marks the B operand as MN-major (its N dimension is the contiguous one in shared memory) instead of K-major.
+constexpr uint32_t umma_idesc_b_mn_major = 1u << 16;
 
 // 32 lanes x 16 consecutive columns of 32-bit values: thread t of the warp gets lane (base lane + t).
 __device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[16]) {

@@ -2,8 +2,10 @@
 //   query_gradient[i, h] += sum_j G_band(h)[i, j] * candidate[j, h],
 // as tcgen05 GEMM tiles of 128 rows x up to 256 channels, the candidate index as the K dimension in stages of 64.
 // A channel tile never crosses a band edge (edges are multiples of 16 channels and a tile is a multiple of 16 wide),
-// so its A operand is a single band's cube. Candidates arrive transposed ([H, R], K-major rows of candidates), the
-// cube through a three-dimensional TMA map.
+// so its A operand is a single band's cube, read through a three-dimensional TMA map. The candidates are the B operand
+// in one of two layouts: as they are, [R, H] row-major, read in boxes of 64 channels x 64 candidates and handed to the
+// tensor cores as an MN-major operand (the channels, the GEMM's N, are the contiguous dimension), which needs no copy of
+// the block; or transposed, [H, R], K-major, for callers that hold them that way.
 //
 // A CTA owns one or two 128-row blocks of a strip (two when there are enough strips to fill the GPU): both blocks use
 // the same candidate stage, which halves the candidate refills from L2, the traffic this kernel is bound by.
@@ -72,6 +74,14 @@ struct bwd_params {
     bwd_tile tiles[bwd_max_tiles];
 };
 
+// Shared-memory descriptor words of the B operand. K-major (transposed candidates): rows of 64 candidates, eight rows
+// per 1024-byte swizzle atom, atoms 1024 bytes apart along N; a step of 16 candidates adds 32 bytes. MN-major (row-major
+// candidates): a box is 64 candidates (K) x 64 channels (N, contiguous, one 128-byte row per candidate); eight
+// candidates make one atom, atoms follow each other every 1024 bytes along K (the stride offset), boxes of 64 channels
+// every 8192 bytes along N (the leading offset); a step of 16 candidates is two atoms, 2048 bytes.
+constexpr uint32_t bwd_mn_box_bytes = 64 * bwd_depth * 2;
+
+template <bool mn_major_>
 __global__ void __launch_bounds__(bwd_threads, 1)
     backward_kernel(const __grid_constant__ CUtensorMap cube_map, const __grid_constant__ bwd_candidate_boxes candidates,
                     const bwd_params p) {
@@ -121,7 +131,8 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     if (warp == 4) {
         bool const elected = elect_one();
         uint32_t stage = 0, phase = 0;
-        uint32_t const bytes = blocks * bwd_a_bytes + tile.width * bwd_depth * 2;
+        uint32_t const boxes = (tile.width + 63u) / 64u; // MN-major: whole boxes of 64 channels, the last one partly used
+        uint32_t const bytes = blocks * bwd_a_bytes + (mn_major_ ? boxes * bwd_mn_box_bytes : tile.width * bwd_depth * 2);
         for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tail->stage_empty[stage]), phase ^ 1u, ctx, site_bwd_stage_empty, chunk)))
                 break;
@@ -132,15 +143,23 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                 for (uint32_t block = 0; block < blocks; ++block)
                     tma_load_3d(destination + block * bwd_a_bytes, &cube_map, full, static_cast<int>(chunk * bwd_depth),
                                 static_cast<int>((first_block + block) * bwd_rows), static_cast<int>(tile.band));
-                // Largest boxes first; 16 channels are 2048 bytes of the stage (rows of 128 bytes under the swizzle).
-                uint32_t done = 0;
+                if constexpr (mn_major_) {
+                    // Boxes of 64 channels x 64 candidates straight from the row-major block; channels past the tile (or
+                    // past the tensor, which the load fills with zeros) are carried along and never multiplied.
+                    for (uint32_t box = 0; box < boxes; ++box)
+                        tma_load_2d(destination + b_offset + box * bwd_mn_box_bytes, &candidates.maps[0], full,
+                                    static_cast<int>(tile.channel0 + box * 64u), static_cast<int>(chunk * bwd_depth));
+                } else {
+                    // Largest boxes first; 16 channels are 2048 bytes of the stage (rows of 128 bytes under the swizzle).
+                    uint32_t done = 0;
 #pragma unroll
-                for (int index = static_cast<int>(bwd_candidate_maps) - 1; index >= 0; --index) {
-                    uint32_t const box = 16u << index;
-                    if (tile.width - done >= box) {
-                        tma_load_2d(destination + b_offset + done * 128u, &candidates.maps[index], full,
-                                    static_cast<int>(chunk * bwd_depth), static_cast<int>(tile.channel0 + done));
-                        done += box;
+                    for (int index = static_cast<int>(bwd_candidate_maps) - 1; index >= 0; --index) {
+                        uint32_t const box = 16u << index;
+                        if (tile.width - done >= box) {
+                            tma_load_2d(destination + b_offset + done * 128u, &candidates.maps[index], full,
+                                        static_cast<int>(chunk * bwd_depth), static_cast<int>(tile.channel0 + done));
+                            done += box;
+                        }
                     }
                 }
             }
@@ -149,9 +168,12 @@ __global__ void __launch_bounds__(bwd_threads, 1)
         }
     } else if (warp == 5) {
         bool const elected = elect_one();
-        uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width);
+        uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width) | (mn_major_ ? umma_idesc_b_mn_major : 0u);
         constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
         uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
+        // The B operand's leading offset (bits 16-29 of the low word) and its advance per 16 candidates.
+        constexpr uint32_t b_leading = mn_major_ ? ((bwd_mn_box_bytes >> 4) << 16) : (1u << 16);
+        constexpr uint32_t b_step = mn_major_ ? (2048u >> 4) : 2u;
         uint32_t stage = 0, phase = 0, accumulate = 0;
         bool ok = true;
         for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
@@ -159,13 +181,13 @@ __global__ void __launch_bounds__(bwd_threads, 1)
             if (!ok) break;
             tcgen05_fence_after();
             uint32_t const a_low = low_base + ((stage * stage_bytes) >> 4);
-            uint32_t const b_low = a_low + (b_offset >> 4);
+            uint32_t const b_low = (a_low & 0xFFFFu) + (b_offset >> 4) + b_leading;
             for (uint32_t block = 0; block < blocks; ++block) {
 #pragma unroll
                 for (uint32_t step = 0; step < bwd_depth / 16; ++step) {
                     uint64_t a_descriptor, b_descriptor;
                     asm("mov.b64 %0, {%1, %2};" : "=l"(a_descriptor) : "r"(a_low + block * (bwd_a_bytes >> 4) + step * 2u), "r"(descriptor_high));
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(b_descriptor) : "r"(b_low + step * 2u), "r"(descriptor_high));
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(b_descriptor) : "r"(b_low + step * b_step), "r"(descriptor_high));
                     if (elected)
                         umma_bf16(tmem_base + block * bwd_block_columns, a_descriptor, b_descriptor, idesc,
                                   step == 0 ? accumulate : 1u);
@@ -186,6 +208,9 @@ __global__ void __launch_bounds__(bwd_threads, 1)
             float* destination = p.query_gradient + static_cast<size_t>(row) * p.hidden + tile.channel0;
             uint32_t const lane_base = tmem_base + ((warp * 32u) << 16) + block * bwd_block_columns;
             for (uint32_t column = 0; column < tile.width; column += 16) {
+                if (!SC_WARP_IN_BOUNDS(static_cast<size_t>(row) * p.hidden + tile.channel0 + column + 15,
+                                       static_cast<size_t>(p.rows_q) * p.hidden))
+                    break;
                 uint32_t values[16];
                 tmem_load_16(lane_base + column, values);
                 tmem_load_wait();
@@ -242,6 +267,9 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
             bwd_tile const held = p.tiles[j - 1];
             p.tiles[j - 1] = p.tiles[j], p.tiles[j] = held;
         }
+    bool const mn_major = a.candidates_row_major != nullptr && a.hidden >= 64;
+    if (!mn_major && a.transposed_candidates == nullptr) throw std::runtime_error("backward: no candidates given");
+    // Everything above is checked before the first driver or runtime call.
     cuuint64_t const cube_dims[3] = {a.rows_c, a.rows_q, a.ladder.count};
     cuuint64_t const cube_strides[2] = {static_cast<cuuint64_t>(a.rows_c) * 2, static_cast<cuuint64_t>(a.rows_c) * a.rows_q * 2};
     cuuint32_t const cube_box[3] = {bwd_depth, bwd_rows, 1};
@@ -249,6 +277,11 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     bwd_candidate_boxes candidates;
     for (uint32_t index = 0; index < bwd_candidate_maps; ++index) {
+        if (mn_major) {
+            // One map over the block as it lies in memory: boxes of 64 channels (the contiguous dimension) x 64 candidates.
+            candidates.maps[index] = cached_operand_map(a.candidates_row_major, a.hidden, a.rows_c, 64, bwd_depth);
+            continue;
+        }
         // A box may not be taller than the tensor; such a box is never asked for either (tiles are at most `hidden` wide).
         uint32_t const channels = 16u << index;
         candidates.maps[index] =
@@ -260,7 +293,9 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     int device = 0;
     cudaGetDevice(&device);
     if (prepared_device != device) {
-        require(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
+        require(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
+                "raising the backward kernel's shared memory");
+        require(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
                 "raising the backward kernel's shared memory");
         cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
         prepared_device = device;
@@ -269,17 +304,20 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     uint32_t const row_blocks = a.rows_q / bwd_rows;
     p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
     dim3 const grid((row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, p.tile_count, a.split);
-    backward_kernel<<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
+    if (mn_major) backward_kernel<true><<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
+    else backward_kernel<false><<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
     cudaError_t const error = cudaGetLastError();
     if (error != cudaSuccess) throw std::runtime_error(std::string("backward launch failed: ") + cudaGetErrorString(error));
     note_launch();
 }
 
 void preload_forward_kernels();
+SC_DEFINE_BOUNDS_READER(bounds_record_backward)
 
 void preload_loss_kernels() {
     cudaFuncAttributes attributes;
-    require(cudaFuncGetAttributes(&attributes, backward_kernel), "preload backward");
+    require(cudaFuncGetAttributes(&attributes, backward_kernel<false>), "preload backward");
+    require(cudaFuncGetAttributes(&attributes, backward_kernel<true>), "preload backward (row-major candidates)");
     preload_forward_kernels();
 }
 

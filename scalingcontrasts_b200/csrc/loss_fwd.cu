@@ -457,11 +457,16 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
 #pragma unroll
         for (int j = 0; j < ahead_count; ++j) {
             uint32_t const index = lane + 32 * j; // (prefix, column) = (index / warp_columns, index % warp_columns)
-            if (index < norm_count)
+            if (index < norm_count &&
+                SC_IN_BOUNDS(static_cast<size_t>(index / warp_columns) * p.rows_c + column_tile * fwd_cols + group * warp_columns +
+                                 index % warp_columns,
+                             static_cast<size_t>(prefixes_) * p.rows_c))
                 ahead[j] = __ldg(p.c_inv + static_cast<size_t>(index / warp_columns) * p.rows_c + column_tile * fwd_cols +
                                  group * warp_columns + index % warp_columns);
         }
-        if (lane < prefixes_) ahead_max = __ldg(p.c_tile_max + static_cast<size_t>(lane) * column_tiles + column_tile);
+        if (lane < prefixes_ &&
+            SC_IN_BOUNDS(static_cast<size_t>(lane) * column_tiles + column_tile, static_cast<size_t>(prefixes_) * column_tiles))
+            ahead_max = __ldg(p.c_tile_max + static_cast<size_t>(lane) * column_tiles + column_tile);
     };
     auto park = [&](uint32_t into) {
 #pragma unroll
@@ -501,7 +506,10 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             float* const destination = p.gradient +
                                        (static_cast<size_t>(item / p.runs_per_strip) * fwd_rows + row_local) * p.hidden +
                                        ((word >> 4) & 0xFFFu) * 16u;
-            fz_drain_chunks(destination, word >> 16, tmem_base + ((quadrant * 32u) << 16) + fz_accumulator_column, group,
+            if (SC_WARP_IN_BOUNDS((static_cast<size_t>(item / p.runs_per_strip) * fwd_rows + row_local) * p.hidden +
+                                      ((word >> 4) & 0xFFFu) * 16u + (word >> 16) * 16u - 1,
+                                  static_cast<size_t>(p.rows_q) * p.hidden))
+                fz_drain_chunks(destination, word >> 16, tmem_base + ((quadrant * 32u) << 16) + fz_accumulator_column, group,
                             p.gradient_scale);
             tcgen05_fence_before();
             __syncwarp();
@@ -800,6 +808,8 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
             // One partial record per (run, column group, row); the 1/N weight and the mirror cell's factor two go in here.
             uint32_t const slot = run * fwd_column_groups + group;
             float* record = p.partials + static_cast<size_t>(slot) * quantities * p.rows_q + row;
+            if (SC_IN_BOUNDS((static_cast<size_t>(slot) * quantities + quantities - 1) * p.rows_q + row,
+                             static_cast<size_t>(p.runs_per_strip) * fwd_column_groups * quantities * p.rows_q)) {
             record[0] = p.weight * g;
             record[static_cast<size_t>(1) * p.rows_q] = p.weight * (ga - bias * g);
 #pragma unroll
@@ -807,6 +817,7 @@ __device__ __forceinline__ void epilogue_role(CUtensorMap const* cube_map, fwd_p
                 record[static_cast<size_t>(2 + k) * p.rows_q] = p.weight * mine[(prefixes_ + k) * fwd_epilogue_threads];
                 record[static_cast<size_t>(2 + prefixes_ + k) * p.rows_q] =
                     2.0f * p.weight * mine[(2 * prefixes_ + k) * fwd_epilogue_threads];
+            }
             }
             if constexpr (fused_) {
                 // The item's patches of this warp are in memory once its bulk stores have completed (not merely been
@@ -1158,6 +1169,16 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     if ((a.pull.bytes[0] | a.pull.bytes[1]) != 0 && blocks < a.multiprocessors / 2) blocks = a.multiprocessors / 2;
     if (blocks < 1) blocks = 1;
 
+    if (a.fused) {
+        if (!forward_fused_supported(a.hidden, a.ladder.count))
+            throw std::runtime_error("forward: the fused kernel takes ladders of at most six prefixes");
+        if (a.tiles_per_run > fz_max_tiles_per_run) throw std::runtime_error("forward: a fused run holds at most 16 tiles");
+        if (a.fused_scratch_bytes < forward_fused_scratch_bytes(a.ladder.count, a.tiles_per_run, blocks))
+            throw std::runtime_error("forward: the fused kernel's scratch is too small");
+        if (a.fused_scratch_bf16 == nullptr || a.transposed_candidates == nullptr || a.query_gradient == nullptr)
+            throw std::runtime_error("forward: the fused kernel needs its scratch, the transposed candidates and the gradient");
+    }
+    // Everything above is checked before the first driver or runtime call.
     CUtensorMap const& q_map = operand_map(a.queries_bf16, a.hidden, a.rows_q, fwd_depth, fwd_rows);
     CUtensorMap const& c_map = operand_map(a.candidates_bf16, a.hidden, a.rows_c, fwd_depth, fwd_cols);
     fz_maps gemm_maps{};
@@ -1170,13 +1191,6 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
             cached_map(a.gradient_cube_bf16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE);
         launch_for_count<false>(a.ladder.count, q_map, c_map, cube_map, gemm_maps, p, blocks, stream);
     } else {
-        if (!forward_fused_supported(a.hidden, a.ladder.count))
-            throw std::runtime_error("forward: the fused kernel takes ladders of at most six prefixes");
-        if (a.tiles_per_run > fz_max_tiles_per_run) throw std::runtime_error("forward: a fused run holds at most 16 tiles");
-        if (a.fused_scratch_bytes < forward_fused_scratch_bytes(a.ladder.count, a.tiles_per_run, blocks))
-            throw std::runtime_error("forward: the fused kernel's scratch is too small");
-        if (a.fused_scratch_bf16 == nullptr || a.transposed_candidates == nullptr || a.query_gradient == nullptr)
-            throw std::runtime_error("forward: the fused kernel needs its scratch, the transposed candidates and the gradient");
         p.gradient = a.query_gradient, p.gradient_scale = a.gradient_scale;
         for (uint32_t band = 0, begin = 0; band < a.ladder.count; begin = a.ladder.ends[band++])
             for (uint32_t channel = begin; channel < a.ladder.ends[band]; channel += fz_max_width) {
@@ -1207,6 +1221,8 @@ void launch_forward(forward_arguments const& a, cudaStream_t stream) {
     if (error != cudaSuccess) throw std::runtime_error(std::string("forward launch failed: ") + cudaGetErrorString(error));
     note_launch();
 }
+
+SC_DEFINE_BOUNDS_READER(bounds_record_forward)
 
 void preload_forward_kernels() {
     cudaFuncAttributes attributes;

@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(256)
     uint32_t const vectors = hidden / 8;
     float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (uint32_t v = lane; v < vectors; v += 32) {
+        if (!SC_IN_BOUNDS(static_cast<size_t>(row) * vectors + v, static_cast<size_t>(row_count) * vectors)) continue;
         uint4 const packed = rows[static_cast<size_t>(row) * vectors + v];
         if (copy != nullptr) copy[static_cast<size_t>(row) * vectors + v] = packed;
         uint32_t const words[4] = {packed.x, packed.y, packed.z, packed.w};
@@ -69,7 +70,8 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xFFFFFFFFu, total, offset);
         running += total;
-        if (lane == 0) inverse_norms[static_cast<size_t>(band) * row_count + row] = running > 0.0f ? rsqrtf(running) : 0.0f;
+        if (lane == 0 && SC_IN_BOUNDS(static_cast<size_t>(band) * row_count + row, static_cast<size_t>(ladder.count) * row_count))
+            inverse_norms[static_cast<size_t>(band) * row_count + row] = running > 0.0f ? rsqrtf(running) : 0.0f;
     }
 }
 
@@ -82,6 +84,7 @@ __global__ void tile_max_kernel(float const* __restrict__ inverse_norms, float* 
     if (index >= tiles * bands) return;
     uint32_t const band = index / tiles, tile = index % tiles;
     float const* base = inverse_norms + static_cast<size_t>(band) * row_count + tile * 64;
+    if (!SC_IN_BOUNDS(static_cast<size_t>(band) * row_count + tile * 64 + lane + 32, static_cast<size_t>(bands) * row_count)) return;
     float value = fmaxf(base[lane], base[lane + 32]);
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) value = fmaxf(value, __shfl_xor_sync(0xFFFFFFFFu, value, offset));
@@ -94,13 +97,16 @@ __global__ void __launch_bounds__(256)
     uint32_t const column = blockIdx.x * 32 + threadIdx.x;
     for (uint32_t r = threadIdx.y; r < 32; r += 8) {
         uint32_t const row = blockIdx.y * 32 + r;
-        if (row < rows && column < hidden) tile[r][threadIdx.x] = in[static_cast<size_t>(row) * hidden + column];
+        if (row < rows && column < hidden && SC_IN_BOUNDS(static_cast<size_t>(row) * hidden + column, static_cast<size_t>(rows) * hidden))
+            tile[r][threadIdx.x] = in[static_cast<size_t>(row) * hidden + column];
     }
     __syncthreads();
     uint32_t const out_column = blockIdx.y * 32 + threadIdx.x;
     for (uint32_t r = threadIdx.y; r < 32; r += 8) {
         uint32_t const out_row = blockIdx.x * 32 + r;
-        if (out_row < hidden && out_column < rows) out[static_cast<size_t>(out_row) * rows + out_column] = tile[threadIdx.x][r];
+        if (out_row < hidden && out_column < rows &&
+            SC_IN_BOUNDS(static_cast<size_t>(out_row) * rows + out_column, static_cast<size_t>(rows) * hidden))
+            out[static_cast<size_t>(out_row) * rows + out_column] = tile[threadIdx.x][r];
     }
 }
 
@@ -131,7 +137,8 @@ __global__ void __launch_bounds__(256)
     float total = 0;
 #pragma unroll 8
     for (uint32_t slot = 0; slot < slots; ++slot)
-        total += partials[(static_cast<size_t>(slot) * quantities + quantity) * rows + row];
+        if (SC_IN_BOUNDS((static_cast<size_t>(slot) * quantities + quantity) * rows + row, static_cast<size_t>(slots) * quantities * rows))
+            total += partials[(static_cast<size_t>(slot) * quantities + quantity) * rows + row];
     accumulators[static_cast<size_t>(quantity) * rows + row] += total;
 }
 
@@ -159,6 +166,7 @@ __global__ void __launch_bounds__(128)
         uint32_t band = 0;
         while (band + 1 < ladder.count && channel >= ladder.ends[band]) ++band;
         float const fold = fold_from[band];
+        if (!SC_IN_BOUNDS(static_cast<size_t>(row) * hidden + channel + 7, static_cast<size_t>(rows) * hidden)) continue;
         uint4 const packed = queries[static_cast<size_t>(row) * vectors + v];
         float4 const g0 = *reinterpret_cast<float4 const*>(query_gradient + static_cast<size_t>(row) * hidden + channel);
         float4 const g1 = *reinterpret_cast<float4 const*>(query_gradient + static_cast<size_t>(row) * hidden + channel + 4);
@@ -270,6 +278,9 @@ __global__ void scale_cast_kernel(float const* __restrict__ src, __nv_bfloat16* 
 int blocks_of(size_t items, int per_block) { return static_cast<int>((items + per_block - 1) / per_block); }
 
 } // namespace
+
+bool bounds_build() { return SC_BOUNDS != 0; }
+SC_DEFINE_BOUNDS_READER(bounds_record_small)
 
 void launch_prefix_norms(void const* rows_bf16, void* copy_bf16, float* inverse_norms, float* tile_max, uint32_t rows,
                          uint32_t hidden, ladder_host const& ladder, cudaStream_t stream) {

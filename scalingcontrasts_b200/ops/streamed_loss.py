@@ -105,7 +105,8 @@ class StreamedLoss:
 
     def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, device=None,
                  candidate_rows: Optional[int] = None, budget_s: float = 2.0, backward_split: int = 0,
-                 fused: Optional[bool] = None, tiles_per_run: Optional[int] = None) -> None:
+                 fused: Optional[bool] = None, tiles_per_run: Optional[int] = None,
+                 transpose_candidates: Optional[bool] = None) -> None:
         ladder.check_device_shape(rows, hidden)
         self.rows, self.hidden, self.ladder, self.spec = rows, hidden, ladder, spec
         self.candidate_rows = rows if candidate_rows is None else candidate_rows
@@ -155,6 +156,12 @@ class StreamedLoss:
                                   self.transposed_candidates.data_ptr(), self.query_gradient.data_ptr(),
                                   self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.status.data_ptr(),
                                   self.budget_ns, self.multiprocessors)
+        # The backward kernel reads the candidates as they lie in memory (an MN-major tensor-core operand); the K-major
+        # form with a transposed copy per block remains for the fused kernel and on request.
+        if transpose_candidates is None:
+            transpose_candidates = os.environ.get("SC_LOSS_TRANSPOSE", "1") == "1"
+        self.transpose_candidates = bool(transpose_candidates) or self.fused or hidden < 64
+        self._plan.transpose_candidates = self.transpose_candidates
         self._begun = False
         self._query_norms_view: Optional[BlockNorms] = None
 

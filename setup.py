@@ -27,15 +27,27 @@ if os.environ.get("SC_FWD_TRACE"):
 if os.environ.get("SC_FWD_HELPER_SLEEP"):
     NVCC_FLAGS.append("-DSC_FWD_HELPER_SLEEP=" + os.environ["SC_FWD_HELPER_SLEEP"])
 
+EXTENSIONS = [CUDAExtension(
+    name="scalingcontrasts_b200._C",
+    sources=SOURCES,
+    include_dirs=[os.path.join(ROOT, CSRC)],
+    extra_compile_args={"cxx": ["-O2", "-std=c++17"], "nvcc": NVCC_FLAGS},
+)]
+# The bounds-checked debug build of the same sources (every computed global index is compared with its limit; a miss is
+# recorded and skipped, never trapped): `SC_NATIVE_VARIANT=bounds` makes the package load it instead of `_C`.
+# SC_BUILD_BOUNDS=0 leaves it out.
+if os.environ.get("SC_BUILD_BOUNDS", "1") != "0":
+    EXTENSIONS.append(CUDAExtension(
+        name="scalingcontrasts_b200._C_bounds",
+        sources=SOURCES,
+        include_dirs=[os.path.join(ROOT, CSRC)],
+        extra_compile_args={"cxx": ["-O2", "-std=c++17", "-DSC_BOUNDS=1"], "nvcc": NVCC_FLAGS + ["-DSC_BOUNDS=1"]},
+    ))
+
 setup(
     name="scalingcontrasts_b200",
     version="0.1.0",
     packages=[],
-    ext_modules=[CUDAExtension(
-        name="scalingcontrasts_b200._C",
-        sources=SOURCES,
-        include_dirs=[os.path.join(ROOT, CSRC)],
-        extra_compile_args={"cxx": ["-O2", "-std=c++17"], "nvcc": NVCC_FLAGS},
-    )],
+    ext_modules=EXTENSIONS,
     cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
 )

@@ -27,3 +27,18 @@ def ext():
     if not _ext.available():
         pytest.skip("native extension not built")
     return _ext.native()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """In the bounds-checked debug build (SC_NATIVE_VARIANT=bounds) every kernel compares its computed global indices with
+    their limits and records the first miss; a session that ran the GPU tests under it must end with no miss recorded."""
+    if os.environ.get("SC_NATIVE_VARIANT", "") != "bounds" or not torch.cuda.is_available():
+        return
+    from scalingcontrasts_b200 import _ext
+
+    if not _ext.available():
+        return
+    records = _ext.native().bounds_records()
+    if any(word != 0 for record in records for word in record):
+        print(f"\nbounds-checked build recorded an out-of-range index: {records}")
+        session.exitstatus = 1

@@ -316,3 +316,31 @@ def test_twenty_repeats_of_a_many_tile_step_and_poisoned_scratch(fused):
             assert relative_l2(gradient.float(), first[0].float()) < 1e-3
         else:
             assert torch.equal(gradient, first[0]), f"repeat {repeat}: the gradient changed bits"
+
+
+@pytest.mark.parametrize("rows,hidden,ends", [(256, 768, (48, 96, 192, 384, 768)), (128, 1024, (64, 128, 256, 512, 1024)),
+                                              (128, 256, (16, 80, 256)), (256, 64, (64,))])
+def test_backward_reads_row_major_candidates_like_transposed_ones(ext, rows, hidden, ends):
+    """The backward kernel takes the candidates either transposed ([H, R], a K-major operand) or as they lie in memory
+    ([R, H], handed to the tensor cores as an MN-major operand, no copy). Same cube, same candidates: the same gradient
+    to float32 rounding of the accumulation order, and both equal to the float32 matmul."""
+    _float32_matmul_exact()
+    stream = torch.cuda.current_stream().cuda_stream
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    cube = (torch.randn(len(ends), rows, rows, device="cuda", generator=generator) * 0.1).to(torch.bfloat16)
+    candidates = torch.randn(rows, hidden, device="cuda", generator=generator).to(torch.bfloat16)
+    transposed = candidates.T.contiguous()
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    outcomes = []
+    for row_major in (0, candidates.data_ptr()):
+        gradient = torch.zeros(rows, hidden, device="cuda")
+        ext.backward(cube.data_ptr(), transposed.data_ptr() if row_major == 0 else 0, gradient.data_ptr(), status.data_ptr(), rows,
+                     rows, hidden, list(ends), 1, 0.5, 2_000_000_000, stream, row_major=row_major)
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0
+        outcomes.append(gradient)
+    reference = 0.5 * torch.cat([cube[b].float() @ candidates.float()[:, (0 if b == 0 else ends[b - 1]):ends[b]]
+                                 for b in range(len(ends))], dim=1)
+    assert relative_l2(outcomes[0], reference) < 1e-5
+    assert relative_l2(outcomes[1], reference) < 1e-5
+    assert relative_l2(outcomes[1], outcomes[0]) < 1e-6
