@@ -4,7 +4,7 @@ any order, then ``finish``.
 A rank owns ``rows`` query rows. Each ``score`` runs, on the calling stream,
 
 1. (unless the caller supplies them) the candidates' prefix inverse norms and per-tile maxima,
-2. a transpose of the candidates (the gradient GEMM reads them K-major),
+2. (fused form only) a transpose of the candidates (its gradient GEMM reads them K-major),
 3. the fused tile kernel (tcgen05): segment dots of every band in tensor memory, sigmoid loss, per-row partial sums, and
    the per-band suffix-summed gradient of a work item (a strip of 128 rows against a run of candidate tiles) as
    bfloat16 patches in a per-CTA scratch buffer, which the same CTA folds into the query gradient with a tensor-core
@@ -12,8 +12,11 @@ A rank owns ``rows`` query rows. Each ``score`` runs, on the calling stream,
    same launch pulls the next block from a peer's memory into local staging,
 4. the deterministic fold of the partials.
 
-Ladders of seven or eight prefixes (or ``fused=False``) take the two-kernel form instead: the forward kernel writes the
-bfloat16 gradient cube ``[K, R, R]`` and a separate backward tile kernel folds it.
+The default is the two-kernel form (``fused=False``; the only one for ladders of seven or eight prefixes): the forward
+kernel writes the bfloat16 gradient cube ``[K, R, R]`` and a separate backward tile kernel folds it, reading the candidates
+as they lie in memory (an MN-major tensor-core operand, no transposed copy). The fused form saves the cube's memory
+(0.59 GB of scratch instead of 2.86 GB at 16384 rows) and is about a fifth slower there, because its GEMM has room for only
+two shared-memory stages beside the score pass; so it is a choice, not the default.
 
 ``finish`` folds the L2-normalisation's self term, casts the gradient to bfloat16 and reduces the row summands into
 ``summands`` (any device float32 span of ``SUMMAND_SLOTS`` values, a domain payload included):
@@ -147,7 +150,14 @@ class StreamedLoss:
             self.similarity_gradients = torch.empty(scratch // 2, **bf16)
         else:
             self.similarity_gradients = torch.empty(k, rows, self.candidate_rows, **bf16)
-        self.transposed_candidates = torch.empty(hidden, self.candidate_rows, **bf16)
+        # The backward kernel reads the candidates as they lie in memory (an MN-major tensor-core operand); the K-major
+        # form with a transposed copy per block remains for the fused kernel, for blocks narrower than 64 channels, and
+        # on request (``transpose_candidates=True`` or SC_LOSS_TRANSPOSE=1).
+        if transpose_candidates is None:
+            transpose_candidates = os.environ.get("SC_LOSS_TRANSPOSE", "0") == "1"
+        self.transpose_candidates = bool(transpose_candidates) or self.fused or hidden < 64
+        self.transposed_candidates = (torch.empty(hidden, self.candidate_rows, **bf16) if self.transpose_candidates
+                                      else torch.empty(0, **bf16))
         self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
         # What never changes between blocks lives in a native plan, so that scoring a block is one call into C++.
         self._plan = ext.LossPlan(rows, self.candidate_rows, hidden, list(ladder.ends), self.tiles_per_run, self.partial_slots,
@@ -156,11 +166,6 @@ class StreamedLoss:
                                   self.transposed_candidates.data_ptr(), self.query_gradient.data_ptr(),
                                   self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.status.data_ptr(),
                                   self.budget_ns, self.multiprocessors)
-        # The backward kernel reads the candidates as they lie in memory (an MN-major tensor-core operand); the K-major
-        # form with a transposed copy per block remains for the fused kernel and on request.
-        if transpose_candidates is None:
-            transpose_candidates = os.environ.get("SC_LOSS_TRANSPOSE", "1") == "1"
-        self.transpose_candidates = bool(transpose_candidates) or self.fused or hidden < 64
         self._plan.transpose_candidates = self.transpose_candidates
         self._begun = False
         self._query_norms_view: Optional[BlockNorms] = None
