@@ -97,3 +97,36 @@ def _missing_rank_worker(rank: int, world: int, port: int) -> None:
 
 def test_a_rank_that_never_joins_is_detected_on_the_host():
     _launch(_missing_rank_worker, 2)
+
+
+def _ring_worker(rank: int, world: int, port: int) -> None:
+    import importlib.util
+
+    from scalingcontrasts_b200 import LossSpec, Matryoshka
+    from scalingcontrasts_b200.cpu import oracle, relative_l2
+    from scalingcontrasts_b200.utils.keyed import normal_embeddings
+
+    _init(rank, world, port)
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baselines", "torch_ring_loss.py")
+    spec = importlib.util.spec_from_file_location("torch_ring_loss", path)
+    ring = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ring)
+    rows, hidden, prefixes = 64, 128, 3
+    block = normal_embeddings(rows, hidden, seed=3, rank=rank).float()
+    loss_share, gradient = ring.ring_step(block, ring.prefix_widths(hidden, prefixes), torch.tensor(10.0), torch.tensor(-10.0))
+    blocks = [torch.empty_like(block) for _ in range(world)]
+    gradients = [torch.empty_like(gradient) for _ in range(world)]
+    dist.all_gather(blocks, block)
+    dist.all_gather(gradients, gradient)
+    total = loss_share.clone()
+    dist.all_reduce(total)
+    expected = oracle(torch.cat(blocks), Matryoshka.halvings(hidden, prefixes), 10.0, -10.0, LossSpec("self"))
+    assert abs(float(total) - expected.loss) <= 1e-5 * abs(expected.loss)
+    assert relative_l2(torch.cat(gradients), expected.gradient) < 1e-4
+    dist.destroy_process_group()
+
+
+def test_ring_exchange_baseline_agrees_with_the_oracle():
+    """The plain-torch neighbour-exchange comparator (baselines/torch_ring_loss.py) computes the same loss and row-owned
+    gradient as the float64 oracle: a baseline that is wrong would flatter whatever is compared with it."""
+    _launch(_ring_worker, 3)
