@@ -159,6 +159,17 @@ void launch_backward(backward_arguments const& arguments, cudaStream_t stream);
 
 void preload_loss_kernels();
 
+// -------- projector tower (tower.cu) -----------------------------------------------------------------------------
+// Elementwise passes between the tower's library GEMMs. bfloat16 matrices are row-major with a multiple of 8 columns.
+// `partials` is scratch of tower_partial_blocks(rows) * columns floats; bias gradients leave as bfloat16 (the
+// parameters' dtype), summed in float32 in a fixed order.
+uint32_t tower_partial_blocks(uint32_t rows);
+void launch_gelu_forward(void const* z_bf16, void* h_bf16, size_t scalars, int multiprocessors, cudaStream_t stream);
+void launch_gelu_backward_bias(void const* upstream_bf16, void const* z_bf16, void* dz_bf16, float* partials, void* bias_grad_bf16,
+                               uint32_t rows, uint32_t columns, cudaStream_t stream);
+void launch_column_sums(void const* matrix_bf16, float* partials, void* sums_bf16, uint32_t rows, uint32_t columns,
+                        cudaStream_t stream);
+
 // -------- bounds-checked debug build ----------------------------------------------------------------------------
 // True in the build with -DSC_BOUNDS=1, in which kernels compare every computed global index with its limit. The
 // readers copy out the first recorded miss of each translation unit (eight words, all zero when there was none; always
@@ -168,6 +179,7 @@ void bounds_record_small(uint32_t* out);
 void bounds_record_forward(uint32_t* out);
 void bounds_record_backward(uint32_t* out);
 void bounds_record_collectives(uint32_t* out);
+void bounds_record_tower(uint32_t* out);
 
 // -------- oracle twin (oracle_cpu.cpp) ---------------------------------------------------------------------------
 // Plain triple loop in float64; gradient [n, hidden]; out[0]=loss, out[1]=bias grad, out[2]=log-beta grad,

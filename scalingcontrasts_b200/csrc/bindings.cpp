@@ -262,7 +262,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("BOUNDS_BUILD") = sc::bounds_build();
     m.def("bounds_records", []() {
         // the first out-of-range index each translation unit recorded (all zeros: none); ordinary builds never record
-        std::vector<std::vector<uint32_t>> records(4, std::vector<uint32_t>(8, 0u));
+        std::vector<std::vector<uint32_t>> records(5, std::vector<uint32_t>(8, 0u));
+        sc::bounds_record_tower(records[4].data());
         sc::bounds_record_small(records[0].data());
         sc::bounds_record_forward(records[1].data());
         sc::bounds_record_backward(records[2].data());
@@ -325,6 +326,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }, py::arg("cube"), py::arg("transposed"), py::arg("query_gradient"), py::arg("status"), py::arg("rows_q"), py::arg("rows_c"),
        py::arg("hidden"), py::arg("ends"), py::arg("split"), py::arg("scale"), py::arg("budget_ns"), py::arg("stream"),
        py::arg("row_major") = 0);
+
+    m.def("tower_partial_blocks", &sc::tower_partial_blocks);
+    m.def("gelu_forward", [](uint64_t z, uint64_t h, uint64_t scalars, int sms, uint64_t stream) {
+        sc::launch_gelu_forward(pointer<void>(z), pointer<void>(h), scalars, sms, stream_of(stream));
+    });
+    m.def("gelu_backward_bias", [](uint64_t upstream, uint64_t z, uint64_t dz, uint64_t partials, uint64_t bias_grad, uint32_t rows,
+                                   uint32_t columns, uint64_t stream) {
+        sc::launch_gelu_backward_bias(pointer<void>(upstream), pointer<void>(z), pointer<void>(dz), pointer<float>(partials),
+                                      pointer<void>(bias_grad), rows, columns, stream_of(stream));
+    });
+    m.def("column_sums", [](uint64_t matrix, uint64_t partials, uint64_t sums, uint32_t rows, uint32_t columns, uint64_t stream) {
+        sc::launch_column_sums(pointer<void>(matrix), pointer<float>(partials), pointer<void>(sums), rows, columns, stream_of(stream));
+    });
 
     m.def("keyed_embeddings", [](uint64_t rows, uint32_t row_count, uint32_t hidden, uint64_t salt, float scale, uint64_t stream) {
         sc::launch_keyed_embeddings(pointer<void>(rows), row_count, hidden, salt, scale, stream_of(stream));

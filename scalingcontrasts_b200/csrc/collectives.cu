@@ -351,17 +351,21 @@ __global__ void __launch_bounds__(small_threads)
     }
 }
 
-// How a bandwidth-class collective is cut: vectors in flight per thread and the number of blocks. Few, fat blocks win
-// at small sizes (the rounds' bookkeeping is per block), many at large ones. Both can be forced from the environment
-// (SC_COLLECTIVE_UNROLL = 2, 4 or 8; SC_COLLECTIVE_MAX_BLOCKS) to sweep them.
+// How a bandwidth-class collective is cut: vectors in flight per thread (1, 2, 4 or 8) and the number of blocks (one per
+// multiprocessor at most). Measured: spreading a member's share over more blocks beats more vectors in flight per thread at
+// every size (2 GPUs, 16 MiB all-reduce: 64.4 us with 2 per thread, 67.0 with 4, 67.8 with 8; 128 MiB: 359 / 372 / 389 us;
+// 64 blocks instead of 148 cost a reduce-scatter of 128 MiB 40 %), so a share that fits one vector per thread of a full
+// grid takes one, anything larger two. Both can be forced from the environment (SC_COLLECTIVE_UNROLL,
+// SC_COLLECTIVE_MAX_BLOCKS) to sweep them.
 struct shape_t {
     int unroll, blocks;
 };
 shape_t shape_for(size_t vectors, int multiprocessors) {
     static int const forced_unroll = std::getenv("SC_COLLECTIVE_UNROLL") ? std::atoi(std::getenv("SC_COLLECTIVE_UNROLL")) : 0;
     static int const forced_blocks = std::getenv("SC_COLLECTIVE_MAX_BLOCKS") ? std::atoi(std::getenv("SC_COLLECTIVE_MAX_BLOCKS")) : 0;
-    int unroll = forced_unroll == 2 || forced_unroll == 4 || forced_unroll == 8 ? forced_unroll : 4;
     int const cap = forced_blocks > 0 ? forced_blocks : multiprocessors;
+    int unroll = vectors <= static_cast<size_t>(cap) * collective_threads ? 1 : 2;
+    if (forced_unroll == 1 || forced_unroll == 2 || forced_unroll == 4 || forced_unroll == 8) unroll = forced_unroll;
     size_t const per_block = static_cast<size_t>(collective_threads) * unroll;
     size_t blocks = (vectors + per_block - 1) / per_block;
     if (blocks < 1) blocks = 1;
@@ -387,7 +391,9 @@ size_t vector_scalars(payload_type type) { return type == payload_type::f32 ? 4 
 template <payload_type type_, bool multicast_>
 void launch_all_reduce_shape(shape_t shape, control_view const& control, char* mc, replica_list const& list, size_t first_vector,
                              size_t vectors, float scale, cudaStream_t stream) {
-    if (shape.unroll == 2)
+    if (shape.unroll == 1)
+        all_reduce_kernel<type_, multicast_, 1><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
+    else if (shape.unroll == 2)
         all_reduce_kernel<type_, multicast_, 2><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
     else if (shape.unroll == 8)
         all_reduce_kernel<type_, multicast_, 8><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, first_vector, vectors, scale);
@@ -397,7 +403,9 @@ void launch_all_reduce_shape(shape_t shape, control_view const& control, char* m
 template <payload_type type_, bool multicast_>
 void launch_reduce_scatter_shape(shape_t shape, control_view const& control, char* mc, replica_list const& list, char* mine,
                                  size_t first_vector, size_t shard_vectors, float scale, float* out_f32, cudaStream_t stream) {
-    if (shape.unroll == 2)
+    if (shape.unroll == 1)
+        reduce_scatter_kernel<type_, multicast_, 1><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
+    else if (shape.unroll == 2)
         reduce_scatter_kernel<type_, multicast_, 2><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
     else if (shape.unroll == 8)
         reduce_scatter_kernel<type_, multicast_, 8><<<shape.blocks, collective_threads, 0, stream>>>(control, mc, list, mine, first_vector, shard_vectors, scale, out_f32);
@@ -506,6 +514,10 @@ void preload_collective_kernels() {
     touch(reinterpret_cast<void const*>(&barrier_kernel));
     touch(reinterpret_cast<void const*>(&expect_arrivals_kernel));
 #define SC_TOUCH_SHAPES(kernel)                                                                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 1>));                                           \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, false, 1>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, true, 1>));                                          \
+    touch(reinterpret_cast<void const*>(&kernel<payload_type::bf16, false, 1>));                                         \
     touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 2>));                                           \
     touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 4>));                                           \
     touch(reinterpret_cast<void const*>(&kernel<payload_type::f32, true, 8>));                                           \

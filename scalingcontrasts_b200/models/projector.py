@@ -1,6 +1,12 @@
 """The one-tower projector of the headline training step: ``Linear(in, mid) -> GELU -> Linear(mid, out)`` in bfloat16
-with Xavier-uniform weights and zero biases. Its matrix products are plain library GEMMs (torch / cuBLAS); the
-hand-written kernels of this library live in the loss and the collectives.
+with Xavier-uniform weights and zero biases.
+
+Its matrix products are plain library GEMMs (torch / cuBLAS, biases folded into the forward GEMMs' epilogues). What sits
+between them is this library's own (``csrc/tower.cu``): on a GPU the module runs as one autograd function whose
+activation is a single vectorised pass, and whose backward computes ``dz = dh * gelu'(z)`` and the first layer's bias
+gradient in one pass over the activations and the second layer's bias gradient in one pass over the incoming gradient,
+both summed in a fixed order (the step stays bit-reproducible). On CPU tensors, in other dtypes or without the
+extension it is the plain ``nn`` composition.
 
 The reference has no model (README.md:83-84 of the reference lists PyTorch only as a baseline); this is the tower the
 training benchmark puts in front of the loss.
@@ -11,13 +17,48 @@ import torch
 from torch import nn
 
 
+class _FusedTower(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight1, bias1, weight2, bias2):
+        from .._ext import native
+
+        ext, stream = native(), torch.cuda.current_stream().cuda_stream
+        z = torch.addmm(bias1, x, weight1.t())
+        h = torch.empty_like(z)
+        ext.gelu_forward(z.data_ptr(), h.data_ptr(), z.numel(), torch.cuda.get_device_properties(x.device).multi_processor_count,
+                         stream)
+        y = torch.addmm(bias2, h, weight2.t())
+        ctx.save_for_backward(x, weight1, weight2, z, h)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .._ext import native
+
+        x, weight1, weight2, z, h = ctx.saved_tensors
+        ext, stream = native(), torch.cuda.current_stream().cuda_stream
+        dy = dy.contiguous()
+        rows, mid, out = x.shape[0], weight1.shape[0], weight2.shape[0]
+        partials = torch.empty(int(ext.tower_partial_blocks(rows)) * max(mid, out), dtype=torch.float32, device=x.device)
+        dbias2 = torch.empty(out, dtype=dy.dtype, device=x.device)
+        ext.column_sums(dy.data_ptr(), partials.data_ptr(), dbias2.data_ptr(), rows, out, stream)
+        dweight2 = dy.t() @ h
+        dh = dy @ weight2
+        dbias1 = torch.empty(mid, dtype=dy.dtype, device=x.device)
+        ext.gelu_backward_bias(dh.data_ptr(), z.data_ptr(), dh.data_ptr(), partials.data_ptr(), dbias1.data_ptr(), rows, mid, stream)
+        dweight1 = dh.t() @ x  # dh now holds dz (written in place, element for element)
+        dx = dh @ weight1 if ctx.needs_input_grad[0] else None
+        return dx, dweight1, dbias1, dweight2, dbias2
+
+
 class Projector(nn.Module):
     def __init__(self, in_features: int = 1024, mid_features: int = 3072, out_features: int = 768,
-                 dtype: torch.dtype = torch.bfloat16, device=None, seed: int = 0) -> None:
+                 dtype: torch.dtype = torch.bfloat16, device=None, seed: int = 0, fused: bool = True) -> None:
         super().__init__()
         self.fc1 = nn.Linear(in_features, mid_features, dtype=dtype, device=device)
         self.act = nn.GELU()
         self.fc2 = nn.Linear(mid_features, out_features, dtype=dtype, device=device)
+        self.fused = fused
         generator = torch.Generator(device="cpu").manual_seed(seed)
         with torch.no_grad():
             for layer in (self.fc1, self.fc2):
@@ -26,7 +67,18 @@ class Projector(nn.Module):
                 layer.weight.copy_(weight.to(dtype))
                 layer.bias.zero_()
 
+    def _can_fuse(self, x: torch.Tensor) -> bool:
+        if not (self.fused and x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous()):
+            return False
+        if self.fc1.weight.dtype != torch.bfloat16 or self.fc1.out_features % 8 or self.fc2.out_features % 8:
+            return False
+        from .._ext import available
+
+        return available()
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._can_fuse(x):
+            return _FusedTower.apply(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
         return self.fc2(self.act(self.fc1(x)))
 
     def flops_per_row(self) -> int:
