@@ -111,15 +111,26 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// 32 columns x 8 row-block groups per block: thread (column, part) adds the partials of row blocks part, part + 8, ... and
+// the eight parts are then added in part order, so the sum's order is fixed whatever the scheduling (and eight loads per
+// column are in flight instead of one dependent chain).
 __global__ void __launch_bounds__(256)
     fold_column_partials_kernel(float const* __restrict__ partials, float* __restrict__ out, uint32_t blocks, uint32_t columns,
                                 void* __restrict__ out_bf16) {
-    uint32_t const column = blockIdx.x * blockDim.x + threadIdx.x;
-    if (column >= columns) return;
+    __shared__ float parts[8][32];
+    uint32_t const lane = threadIdx.x % 32, part = threadIdx.x / 32;
+    uint32_t const column = blockIdx.x * 32 + lane;
     float total = 0;
-    for (uint32_t block = 0; block < blocks; ++block) total += partials[static_cast<size_t>(block) * columns + column];
-    if (out != nullptr) out[column] = total;
-    if (out_bf16 != nullptr) static_cast<__nv_bfloat16*>(out_bf16)[column] = __float2bfloat16(total);
+    if (column < columns)
+        for (uint32_t block = part; block < blocks; block += 8) total += partials[static_cast<size_t>(block) * columns + column];
+    parts[part][lane] = total;
+    __syncthreads();
+    if (part != 0 || column >= columns) return;
+    float folded = 0;
+#pragma unroll
+    for (int other = 0; other < 8; ++other) folded += parts[other][lane];
+    if (out != nullptr) out[column] = folded;
+    if (out_bf16 != nullptr) static_cast<__nv_bfloat16*>(out_bf16)[column] = __float2bfloat16(folded);
 }
 
 void check_launch(char const* what) {
@@ -154,7 +165,7 @@ void launch_gelu_backward_bias(void const* upstream_bf16, void const* z_bf16, vo
     column_partials_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint4 const*>(upstream_bf16), static_cast<uint4 const*>(z_bf16),
                                                             static_cast<uint4*>(dz_bf16), partials, rows, columns);
     check_launch("gelu_backward_bias");
-    fold_column_partials_kernel<<<(columns + 255) / 256, 256, 0, stream>>>(partials, nullptr, grid.y, columns, bias_grad_bf16);
+    fold_column_partials_kernel<<<(columns + 31) / 32, 256, 0, stream>>>(partials, nullptr, grid.y, columns, bias_grad_bf16);
     check_launch("fold_column_partials");
 }
 
@@ -164,7 +175,7 @@ void launch_column_sums(void const* matrix_bf16, float* partials, void* sums_bf1
     dim3 const grid((columns + tower_columns_per_block - 1) / tower_columns_per_block, tower_partial_blocks(rows));
     column_partials_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint4 const*>(matrix_bf16), nullptr, nullptr, partials, rows, columns);
     check_launch("column_sums");
-    fold_column_partials_kernel<<<(columns + 255) / 256, 256, 0, stream>>>(partials, nullptr, grid.y, columns, sums_bf16);
+    fold_column_partials_kernel<<<(columns + 31) / 32, 256, 0, stream>>>(partials, nullptr, grid.y, columns, sums_bf16);
     check_launch("fold_column_partials");
 }
 

@@ -19,9 +19,10 @@ from torch import nn
 
 class _FusedTower(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight1, bias1, weight2, bias2):
+    def forward(ctx, x, weight1, bias1, weight2, bias2, landing):
         from .._ext import native
 
+        ctx.landing = landing
         ext, stream = native(), torch.cuda.current_stream().cuda_stream
         z = torch.addmm(bias1, x, weight1.t())
         h = torch.empty_like(z)
@@ -40,15 +41,24 @@ class _FusedTower(torch.autograd.Function):
         dy = dy.contiguous()
         rows, mid, out = x.shape[0], weight1.shape[0], weight2.shape[0]
         partials = torch.empty(int(ext.tower_partial_blocks(rows)) * max(mid, out), dtype=torch.float32, device=x.device)
-        dbias2 = torch.empty(out, dtype=dy.dtype, device=x.device)
+
+        def landing(name, shape):
+            # Where a parameter's gradient should be produced: a fresh alias of the buffer a gradient reducer named (so
+            # that autograd adopts it as `.grad` and nothing is copied afterwards), or new memory.
+            target = None if ctx.landing is None else ctx.landing.get(name)
+            if target is not None and tuple(target.shape) == tuple(shape) and target.dtype == dy.dtype:
+                return target.view(target.shape)
+            return torch.empty(shape, dtype=dy.dtype, device=x.device)
+
+        dbias2 = landing("fc2.bias", (out,))
         ext.column_sums(dy.data_ptr(), partials.data_ptr(), dbias2.data_ptr(), rows, out, stream)
-        dweight2 = dy.t() @ h
+        dweight2 = torch.mm(dy.t(), h, out=landing("fc2.weight", (out, mid)))
         dh = dy @ weight2
-        dbias1 = torch.empty(mid, dtype=dy.dtype, device=x.device)
+        dbias1 = landing("fc1.bias", (mid,))
         ext.gelu_backward_bias(dh.data_ptr(), z.data_ptr(), dh.data_ptr(), partials.data_ptr(), dbias1.data_ptr(), rows, mid, stream)
-        dweight1 = dh.t() @ x  # dh now holds dz (written in place, element for element)
+        dweight1 = torch.mm(dh.t(), x, out=landing("fc1.weight", (mid, x.shape[1])))  # dh now holds dz (written in place)
         dx = dh @ weight1 if ctx.needs_input_grad[0] else None
-        return dx, dweight1, dbias1, dweight2, dbias2
+        return dx, dweight1, dbias1, dweight2, dbias2, None
 
 
 class Projector(nn.Module):
@@ -59,6 +69,9 @@ class Projector(nn.Module):
         self.act = nn.GELU()
         self.fc2 = nn.Linear(mid_features, out_features, dtype=dtype, device=device)
         self.fused = fused
+        # Optional: parameter name -> buffer in which that parameter's gradient should be produced (a gradient reducer's
+        # bucket slots, see GradientReducer.landing_buffers); used by the fused path only.
+        self.gradient_landing = None
         generator = torch.Generator(device="cpu").manual_seed(seed)
         with torch.no_grad():
             for layer in (self.fc1, self.fc2):
@@ -78,7 +91,7 @@ class Projector(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self._can_fuse(x):
-            return _FusedTower.apply(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+            return _FusedTower.apply(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias, self.gradient_landing)
         return self.fc2(self.act(self.fc1(x)))
 
     def flops_per_row(self) -> int:

@@ -82,6 +82,14 @@ class GradientReducer:
                 total += -(-parameter.numel() * parameter.element_size() // 16) * 16 + 256
         return total + 4096
 
+    def landing_buffers(self, module: torch.nn.Module) -> dict:
+        """Parameter name -> this reducer's bucket slot for it. A backward pass that writes a gradient straight into its
+        slot (and hands autograd an alias of it) saves the copy the hook would otherwise make."""
+        if not self.enabled:
+            return {}
+        return {name: self._by_parameter[id(parameter)][1] for name, parameter in module.named_parameters()
+                if id(parameter) in self._by_parameter}
+
     def _on_gradient(self, parameter: torch.nn.Parameter) -> None:
         bucket, view = self._by_parameter[id(parameter)]
         if parameter.grad.data_ptr() != view.data_ptr():

@@ -44,6 +44,7 @@ class ContrastiveTrainer:
         self.loss.engine.use_graphs = graphs
         # Every rank's loss is the world's sum and row gradients are final, so parameter gradients are summed.
         self.reducer = GradientReducer(self.projector.parameters(), self.domain, scale=1.0)
+        self.projector.gradient_landing = self.reducer.landing_buffers(self.projector) or None
         parameters = list(self.projector.parameters()) + list(self.loss.parameters())
         if optimizer == "adamw":
             self.optimizer = torch.optim.AdamW(parameters, lr=lr, weight_decay=weight_decay, fused=True)

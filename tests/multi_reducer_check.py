@@ -21,7 +21,11 @@ def main() -> None:
     for step in range(3):
         x = torch.randn(256, 64, generator=torch.Generator().manual_seed(100 * step + rank)).to(device, torch.bfloat16)
         model.zero_grad(set_to_none=True)
+        # odd steps: the tower's backward writes its gradients straight into the reducer's bucket slots (no copy in the hook)
+        model.gradient_landing = reducer.landing_buffers(model) if step % 2 else None
         model(x).float().square().sum().backward()
+        if step % 2:
+            assert all(p.grad.data_ptr() == reducer.landing_buffers(model)[n].data_ptr() for n, p in model.named_parameters())
         reducer.wait()
         torch.cuda.synchronize()
         # the same backward without hooks, summed by NCCL in float32

@@ -53,3 +53,23 @@ def test_fused_tower_is_bit_reproducible():
         runs.append([y.clone()] + [p.grad.clone() for p in tower.parameters()])
     for later in runs[1:]:
         assert all(torch.equal(a, b) for a, b in zip(runs[0], later))
+
+
+def test_gradients_land_in_named_buffers_without_a_copy():
+    """With ``gradient_landing`` set (a gradient reducer's bucket slots), the tower's backward produces each parameter's
+    gradient in that buffer and autograd adopts it: same values as without, and `.grad` points into the buffer."""
+    from scalingcontrasts_b200.models.projector import Projector
+
+    tower = Projector(64, 256, 128, device="cuda", seed=7)
+    x = torch.randn(512, 64, device="cuda").to(torch.bfloat16)
+    upstream = torch.randn(512, 128, device="cuda").to(torch.bfloat16)
+    tower(x).backward(upstream)
+    expected = {name: parameter.grad.clone() for name, parameter in tower.named_parameters()}
+    buffers = {name: torch.full_like(parameter, float("nan")) for name, parameter in tower.named_parameters()}
+    tower.gradient_landing = buffers
+    for _ in range(2):  # the second step rewrites the same buffers
+        tower.zero_grad(set_to_none=True)
+        tower(x).backward(upstream)
+        for name, parameter in tower.named_parameters():
+            assert parameter.grad.data_ptr() == buffers[name].data_ptr(), name
+            assert torch.equal(parameter.grad, expected[name]), name
