@@ -65,6 +65,10 @@ class ContrastiveTrainer:
         if hasattr(self.domain, "status_view"):
             self._status_sources += [self.domain.status_view(0), self.domain.status_view(1)]
         self._status_host = torch.zeros(2, len(self._status_sources), 8, dtype=torch.int32).pin_memory()
+        # One report per step: the summands and the status blocks are gathered into one device buffer by the library's
+        # span-copy kernel (two spans per launch) and cross to the host as a single copy.
+        self._report = torch.zeros(16 + 8 * len(self._status_sources), dtype=torch.int32, device=self.device)
+        self._report_host = torch.zeros(2, self._report.numel(), dtype=torch.int32).pin_memory()
         self._loss_events = [torch.cuda.Event(), torch.cuda.Event()]
         self._loss_pending: Deque[int] = deque()
         for event in self._slot_free:
@@ -99,12 +103,23 @@ class ContrastiveTrainer:
         self._slot_free[slot].record()
         previous = self._collect_loss()
         index = self.steps_done % 2
-        self._loss_host[index, :12].copy_(self.loss.last_summands, non_blocking=True)
-        for position, source in enumerate(self._status_sources):
-            self._status_host[index, position].copy_(source, non_blocking=True)
+        self._gather_report()
+        self._report_host[index].copy_(self._report, non_blocking=True)
         self._loss_events[index].record()
         self._loss_pending.append(index)
         return previous
+
+    def _gather_report(self) -> None:
+        from ._ext import native
+
+        ext, stream = native(), torch.cuda.current_stream().cuda_stream
+        base = self._report.data_ptr()
+        spans = [(self.loss.last_summands.data_ptr(), base, 48)]
+        spans += [(source.data_ptr(), base + 64 + 32 * position, 32) for position, source in enumerate(self._status_sources)]
+        for first in range(0, len(spans), 2):
+            a = spans[first]
+            b = spans[first + 1] if first + 1 < len(spans) else (0, 0, 0)
+            ext.pull(a[0], a[1], a[2], b[0], b[1], b[2], 1, stream)
 
     def step_on_device(self, x: torch.Tensor) -> torch.Tensor:
         """One step on a batch that already lives on the device; returns the loss as a device scalar."""
@@ -126,6 +141,9 @@ class ContrastiveTrainer:
             return None
         index = self._loss_pending.popleft()
         self._loss_events[index].synchronize()
+        report = self._report_host[index]
+        self._loss_host[index, :12] = report[:12].view(torch.float32)
+        self._status_host[index] = report[16:].view(len(self._status_sources), 8)
         codes = self._status_host[index, :, 0].tolist()
         if any(codes):
             names = ["loss kernels", "loss collectives", "gradient reducer"]
@@ -148,7 +166,7 @@ class ContrastiveTrainer:
         return self.rows * self.in_features * 2
 
     def d2h_bytes_per_step(self) -> int:
-        return 12 * 4 + len(self._status_sources) * 8 * 4
+        return self._report.numel() * 4
 
     # -- checkpoints ------------------------------------------------------------------------------------------
     def state_dict(self) -> Dict[str, object]:
