@@ -72,6 +72,10 @@ std::shared_ptr<control_handle> make_control(sc::native_domain const& domain, ui
 
 // Everything about a streamed-loss object that does not change from block to block, so that scoring a block is one
 // call from Python: the transpose, the tile kernel(s) and the fold of the partial sums are enqueued here back to back.
+void runtime_check(cudaError_t result, char const* what) {
+    if (result != cudaSuccess) throw std::runtime_error(std::string(what) + " failed: " + cudaGetErrorString(result));
+}
+
 struct loss_plan {
     uint32_t rows_q = 0, rows_c = 0, hidden = 0;
     sc::ladder_host ladder{};
@@ -84,18 +88,95 @@ struct loss_plan {
 
     bool transpose_candidates = true; // false: the backward kernel reads the block as it lies (MN-major operand)
 
+    // Overlap of one block's backward GEMM with the next block's forward kernel. The two kernels want different parts
+    // of the chip (the forward is bound by its epilogue arithmetic, the backward by memory), so inside a step of
+    // several blocks the backward of block b runs on a second stream on `backward_multiprocessors` multiprocessors while
+    // the forward of block b+1, launched first and with its persistent grid cut by that many, runs on the rest. It takes
+    // a second gradient cube (`gradients_alt`); a block's candidates must stay in place until the block after next is
+    // scored. The last backward of a step runs on the caller's stream in `join`.
+    bool overlap = false;
+    int backward_multiprocessors = 0;
+    uint64_t gradients_alt = 0;
+    // `front` (highest priority) carries the forward kernels and `side` (lowest) the overlapped backward kernels: when
+    // both have blocks waiting for a multiprocessor, the forward's are placed first, whichever kernel started first.
+    cudaStream_t side = nullptr, front = nullptr;
+    cudaEvent_t forward_done[2] = {nullptr, nullptr}, backward_done[2] = {nullptr, nullptr};
+    cudaEvent_t forked[2] = {nullptr, nullptr}, rejoined[2] = {nullptr, nullptr};
+    uint32_t scored = 0;
+    bool pending = false;
+    uint32_t pending_slot = 0;
+    sc::backward_arguments pending_backward{};
+
+    ~loss_plan() {
+        for (cudaEvent_t event : {forward_done[0], forward_done[1], backward_done[0], backward_done[1], forked[0], forked[1],
+                                  rejoined[0], rejoined[1]})
+            if (event) cudaEventDestroy(event);
+        if (side) cudaStreamDestroy(side);
+        if (front) cudaStreamDestroy(front);
+    }
+
+    void enable_overlap(uint64_t second_cube, int reserved) {
+        if (fused) throw std::runtime_error("LossPlan: the fused kernel has no separate backward to overlap");
+        if (reserved < 1 || reserved >= multiprocessors)
+            throw std::runtime_error("LossPlan: the backward's share of the multiprocessors must lie in [1, all)");
+        if (!second_cube) throw std::runtime_error("LossPlan: overlap needs a second gradient cube");
+        if (!side) {
+            int least = 0, greatest = 0;
+            runtime_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "cudaDeviceGetStreamPriorityRange");
+            runtime_check(cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, least), "cudaStreamCreateWithPriority");
+            runtime_check(cudaStreamCreateWithPriority(&front, cudaStreamNonBlocking, greatest), "cudaStreamCreateWithPriority");
+            for (cudaEvent_t* event : {&forward_done[0], &forward_done[1], &backward_done[0], &backward_done[1], &forked[0],
+                                       &forked[1], &rejoined[0], &rejoined[1]})
+                runtime_check(cudaEventCreateWithFlags(event, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+        }
+        gradients_alt = second_cube, backward_multiprocessors = reserved, overlap = true;
+    }
+
+    // Starts a step: no backward is in flight (join() ended the last one).
+    void begin_step() {
+        if (pending) throw std::runtime_error("LossPlan: begin_step with a backward still pending (join() was not called)");
+        scored = 0;
+    }
+
+    void launch_pending_on_side() {
+        runtime_check(cudaStreamWaitEvent(side, forward_done[pending_slot], 0), "cudaStreamWaitEvent");
+        sc::launch_backward(pending_backward, side);
+        runtime_check(cudaEventRecord(backward_done[pending_slot], side), "cudaEventRecord");
+        pending = false;
+    }
+
+    // Ends a step on `stream`: everything the side stream still runs is waited for, and the last block's backward runs
+    // here with the whole chip.
+    void join(uint64_t stream_handle) {
+        cudaStream_t const stream = stream_of(stream_handle);
+        if (overlap && scored >= 2) {
+            // the backward of the block before the last one (and, through stream order, all earlier ones)
+            runtime_check(cudaStreamWaitEvent(stream, backward_done[(scored & 1u)], 0), "cudaStreamWaitEvent");
+        }
+        if (pending) {
+            sc::launch_backward(pending_backward, stream);
+            pending = false;
+        }
+        scored = 0;
+    }
+
     void score(uint64_t queries, uint64_t candidates, uint64_t q_inv, uint64_t c_inv, uint64_t c_tile_max, uint64_t query_base,
                uint64_t candidate_base, float beta, float bias, double live, uint64_t scalars, uint64_t pull_src0,
                uint64_t pull_dst0, uint64_t pull_bytes0, uint64_t pull_src1, uint64_t pull_dst1, uint64_t pull_bytes1,
-               uint64_t stream_handle) const {
+               uint64_t stream_handle) {
         cudaStream_t const stream = stream_of(stream_handle);
         bool const transposing = fused || transpose_candidates || hidden < 64;
+        bool const overlapping = overlap && !transposing;
+        uint32_t const slot = overlapping ? scored & 1u : 0u;
+        uint64_t const cube = slot ? gradients_alt : gradients;
+        // this cube was last read by the backward of the block before the previous one
+        if (overlapping && scored >= 2) runtime_check(cudaStreamWaitEvent(stream, backward_done[slot], 0), "cudaStreamWaitEvent");
         if (transposing) sc::launch_transpose(pointer<void>(candidates), pointer<void>(transposed), rows_c, hidden, stream);
         sc::forward_arguments a{};
         a.queries_bf16 = pointer<void>(queries), a.candidates_bf16 = pointer<void>(candidates);
         a.query_inverse_norms = pointer<float>(q_inv), a.candidate_inverse_norms = pointer<float>(c_inv);
         a.candidate_tile_max = pointer<float>(c_tile_max);
-        a.gradient_cube_bf16 = pointer<void>(gradients), a.partials = pointer<float>(partials);
+        a.gradient_cube_bf16 = pointer<void>(cube), a.partials = pointer<float>(partials);
         a.status = pointer<uint32_t>(status);
         a.rows_q = rows_q, a.rows_c = rows_c, a.hidden = hidden, a.ladder = ladder;
         a.tiles_per_run = tiles_per_run, a.beta = beta, a.bias = bias, a.weight = static_cast<float>(1.0 / live);
@@ -103,22 +184,36 @@ struct loss_plan {
         a.query_base = query_base, a.candidate_base = candidate_base, a.spec_code = spec_code, a.budget_ns = budget_ns;
         a.pull.src[0] = pointer<void>(pull_src0), a.pull.dst[0] = pointer<void>(pull_dst0), a.pull.bytes[0] = pull_bytes0;
         a.pull.src[1] = pointer<void>(pull_src1), a.pull.dst[1] = pointer<void>(pull_dst1), a.pull.bytes[1] = pull_bytes1;
-        a.multiprocessors = multiprocessors;
-        a.fused = fused, a.fused_scratch_bf16 = pointer<void>(gradients), a.fused_scratch_bytes = gradients_bytes;
+        // a forward that has the previous block's backward beside it leaves that kernel its multiprocessors
+        a.multiprocessors = overlapping && pending ? multiprocessors - backward_multiprocessors : multiprocessors;
+        a.fused = fused, a.fused_scratch_bf16 = pointer<void>(cube), a.fused_scratch_bytes = gradients_bytes;
         a.transposed_candidates = pointer<void>(transposed), a.query_gradient = pointer<float>(query_gradient);
         a.gradient_scale = static_cast<float>(2.0 / live);
-        sc::launch_forward(a, stream);
+        if (overlapping && pending) {
+            runtime_check(cudaEventRecord(forked[slot], stream), "cudaEventRecord");
+            runtime_check(cudaStreamWaitEvent(front, forked[slot], 0), "cudaStreamWaitEvent");
+            sc::launch_forward(a, front);
+            // the previous block's backward goes out once this block's forward is in its queue
+            launch_pending_on_side();
+            runtime_check(cudaEventRecord(rejoined[slot], front), "cudaEventRecord");
+            runtime_check(cudaStreamWaitEvent(stream, rejoined[slot], 0), "cudaStreamWaitEvent");
+        } else sc::launch_forward(a, stream);
         sc::launch_fold_partials(pointer<float>(partials), pointer<float>(accumulators), rows_q, partial_slots, quantities, stream);
         if (!fused) {
             sc::backward_arguments b{};
-            b.gradient_cube_bf16 = pointer<void>(gradients);
+            b.gradient_cube_bf16 = pointer<void>(cube);
             b.transposed_candidates = transposing ? pointer<void>(transposed) : nullptr;
             b.candidates_row_major = transposing ? nullptr : pointer<void>(candidates);
             b.query_gradient = pointer<float>(query_gradient), b.status = pointer<uint32_t>(status);
             b.rows_q = rows_q, b.rows_c = rows_c, b.hidden = hidden, b.ladder = ladder, b.split = backward_split;
             b.scale = static_cast<float>(2.0 / live), b.budget_ns = budget_ns;
-            sc::launch_backward(b, stream);
+            if (!overlapping) sc::launch_backward(b, stream);
+            else {
+                runtime_check(cudaEventRecord(forward_done[slot], stream), "cudaEventRecord");
+                pending_backward = b, pending_slot = slot, pending = true;
+            }
         }
+        ++scored;
     }
 };
 
@@ -258,6 +353,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("gradients"), py::arg("gradients_bytes"), py::arg("transposed"), py::arg("query_gradient"),
              py::arg("partials"), py::arg("accumulators"), py::arg("status"), py::arg("budget_ns"), py::arg("multiprocessors"))
         .def_readwrite("transpose_candidates", &loss_plan::transpose_candidates)
+        .def_readonly("overlap", &loss_plan::overlap)
+        .def("enable_overlap", &loss_plan::enable_overlap, py::arg("second_cube"), py::arg("backward_multiprocessors"))
+        .def("begin_step", &loss_plan::begin_step)
+        .def("join", &loss_plan::join, py::arg("stream"))
         .def("score", &loss_plan::score);
     m.attr("BOUNDS_BUILD") = sc::bounds_build();
     m.def("bounds_records", []() {

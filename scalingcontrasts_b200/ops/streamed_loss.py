@@ -109,7 +109,8 @@ class StreamedLoss:
     def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, device=None,
                  candidate_rows: Optional[int] = None, budget_s: float = 2.0, backward_split: int = 0,
                  fused: Optional[bool] = None, tiles_per_run: Optional[int] = None,
-                 transpose_candidates: Optional[bool] = None) -> None:
+                 transpose_candidates: Optional[bool] = None, overlap_backward: Optional[bool] = None,
+                 backward_multiprocessors: Optional[int] = None) -> None:
         ladder.check_device_shape(rows, hidden)
         self.rows, self.hidden, self.ladder, self.spec = rows, hidden, ladder, spec
         self.candidate_rows = rows if candidate_rows is None else candidate_rows
@@ -167,6 +168,22 @@ class StreamedLoss:
                                   self.partials.data_ptr(), self.row_accumulators.data_ptr(), self.status.data_ptr(),
                                   self.budget_ns, self.multiprocessors)
         self._plan.transpose_candidates = self.transpose_candidates
+        # With ``overlap_backward`` a block's gradient GEMM runs on a second stream, on a few multiprocessors, beside the
+        # next block's forward kernel (whose grid shrinks by as many), and a step's last one runs alone in finish(). It
+        # takes a second gradient cube, and the caller must leave a block's candidates in place until the block after
+        # next has been handed to score() (or finish() was called). Results are bit-identical to the in-line order.
+        # Measured on a power-capped B200 it gains nothing (8 blocks of 16384 rows: 15.1 ms at 20 multiprocessors for the
+        # backward, 15.7 at 28, 16.9 at 40, against 15.3 in line), so it is off unless asked for.
+        if overlap_backward is None:
+            overlap_backward = os.environ.get("SC_LOSS_OVERLAP", "0") == "1"
+        self.overlap_backward = bool(overlap_backward) and not self.transpose_candidates
+        self.similarity_gradients_alt = torch.empty(0, **bf16)
+        if self.overlap_backward:
+            if backward_multiprocessors is None:
+                backward_multiprocessors = int(os.environ.get("SC_LOSS_BACKWARD_SMS", "0")) or round(self.multiprocessors * 0.2)
+            self.backward_multiprocessors = max(1, min(int(backward_multiprocessors), self.multiprocessors - 1))
+            self.similarity_gradients_alt = torch.empty_like(self.similarity_gradients)
+            self._plan.enable_overlap(self.similarity_gradients_alt.data_ptr(), self.backward_multiprocessors)
         self._begun = False
         self._query_norms_view: Optional[BlockNorms] = None
 
@@ -174,7 +191,8 @@ class StreamedLoss:
     def bytes(self) -> int:
         """Bytes of scratch this object holds; does not grow with the number of blocks scored."""
         tensors = (self.query_norms.storage, self.candidate_norms.storage, self.query_gradient, self.row_accumulators,
-                   self.partials, self.similarity_gradients, self.transposed_candidates, self.status)
+                   self.partials, self.similarity_gradients, self.similarity_gradients_alt, self.transposed_candidates,
+                   self.status)
         return sum(t.numel() * t.element_size() for t in tensors)
 
     def begin(self, queries: torch.Tensor, stream=None, query_norms: Optional[BlockNorms] = None) -> None:
@@ -188,6 +206,7 @@ class StreamedLoss:
             self._query_norms_view = self.query_norms
         else:
             self._query_norms_view = query_norms
+        self._plan.begin_step()
         self._begun = True
 
     def score(self, queries: torch.Tensor, candidates: torch.Tensor, query_base: int, candidate_base: int, beta: float,
@@ -228,6 +247,7 @@ class StreamedLoss:
             raise ValueError(f"summands must be a contiguous float32 span of at least {SUMMAND_SLOTS} values")
         ext, s = native(), _stream(stream)
         qn = self._query_norms_view
+        self._plan.join(s)
         ext.finalize(queries.data_ptr(), qn.inverse.data_ptr(), self.row_accumulators.data_ptr(),
                      self.query_gradient.data_ptr(), gradient_out.data_ptr(), self.rows, self.hidden, list(self.ladder.ends), s)
         ext.sum_summands(self.row_accumulators.data_ptr(), summands.data_ptr(), self.rows, self.ladder.count, s)

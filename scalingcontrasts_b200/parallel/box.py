@@ -19,6 +19,8 @@ replaces the reference's serial ``cudaMemcpyAsync`` (scalingcontrasts.cuh:1262-1
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
@@ -57,11 +59,19 @@ class BoxLoss:
     """One rank's engine for box-wide loss steps. ``domain`` may be None for a single, unconnected GPU."""
 
     def __init__(self, rows: int, hidden: int, ladder: Matryoshka, spec: LossSpec = REFERENCE_SPEC, domain=None,
-                 device=None, budget_s: float = 2.0) -> None:
+                 device=None, budget_s: float = 2.0, overlap_backward: Optional[bool] = None) -> None:
         self.rows, self.hidden, self.ladder, self.spec, self.domain = rows, hidden, ladder, spec, domain
         self.device = domain.device if domain is not None else (
             torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
-        self.loss = StreamedLoss(rows, hidden, ladder, spec, self.device, budget_s=budget_s)
+        # On request (or SC_LOSS_OVERLAP=1) each block's gradient GEMM runs beside the next block's forward kernel (see
+        # StreamedLoss). Off by default: on a power-capped B200 the two kernels side by side took as long as one after
+        # the other (15.1 against 15.3 ms for eight 16384-row blocks at the best split), for twice the gradient cube.
+        if overlap_backward is None:
+            overlap_backward = os.environ.get("SC_LOSS_OVERLAP", "0") == "1"
+        self.loss = StreamedLoss(rows, hidden, ladder, spec, self.device, budget_s=budget_s, overlap_backward=overlap_backward)
+        # Staging buffers for peers' blocks: with the overlap a block is still read by its gradient GEMM while the block
+        # after it is scored and the one after that is pulled, hence three.
+        self._slots = 3 if self.loss.overlap_backward else 2
         k = ladder.count
         block_bytes = rows * hidden * 2
         if domain is not None:
@@ -79,9 +89,10 @@ class BoxLoss:
             self.summands = torch.zeros(SUMMAND_SLOTS, dtype=torch.float32, device=self.device)
             self.members, self.member = 1, 0
         self.norms = BlockNorms(k, rows, norms_storage)
-        self.staged = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) for _ in range(2)]
-        self.staged_norms = [BlockNorms(k, rows, device=self.device) for _ in range(2)]
+        self.staged = [torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) for _ in range(self._slots)]
+        self.staged_norms = [BlockNorms(k, rows, device=self.device) for _ in range(self._slots)]
         self.gradient = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device)
+        self._cursor = 0
         self.use_graphs = False
         self._graphs = {}
 
@@ -101,25 +112,35 @@ class BoxLoss:
 
     def score_sequence(self, blocks: Sequence[SourceBlock], query_base: int, live: int, beta: float, bias: float,
                        scalars: Optional[torch.Tensor] = None, stream=None) -> None:
-        """Scores ``blocks`` in order. A block in a peer's replica is pulled into one of two staging buffers by the forward
-        launch of the block before it, so only a remote block in first position costs a launch of its own."""
+        """Scores ``blocks`` in order. A block in a peer's replica is pulled into a staging buffer by the forward launch of
+        the block before it, so only a remote block in first position costs a launch of its own. The staging buffers are
+        used in rotation across calls, so that a buffer is written again only once every kernel reading it has finished
+        (two buffers when the gradient GEMM runs in line, three when it overlaps the next block's forward)."""
         from .._ext import native
 
+        ahead = None  # the staging slot that the previous block's launch filled with this block
         for index, block in enumerate(blocks):
             if block.local:
                 candidates, norms = block.embeddings, block.norms
             else:
-                slot = (index - 1) % 2
-                if index == 0:
-                    request = self._pull(block, slot)
+                if ahead is None:
+                    ahead = self._take_slot()
+                    request = self._pull(block, ahead)
                     native().pull(request.src0, request.dst0, request.bytes0, request.src1, request.dst1, request.bytes1,
                                   self.loss.multiprocessors, (torch.cuda.current_stream() if stream is None else stream).cuda_stream)
-                candidates, norms = self.staged[slot], self.staged_norms[slot]
+                candidates, norms = self.staged[ahead], self.staged_norms[ahead]
             following = blocks[index + 1] if index + 1 < len(blocks) else None
-            pull = self._pull(following, index % 2) if following is not None and not following.local else None
+            pull, ahead = None, None
+            if following is not None and not following.local:
+                ahead = self._take_slot()
+                pull = self._pull(following, ahead)
             with phase(f"score block at {block.candidate_base}" + (" + pull of the next" if pull is not None else "")):
                 self.loss.score(self.embeddings, candidates, query_base, block.candidate_base, beta, bias, live, stream,
                                 candidate_norms=norms, scalars=scalars, pull_next=pull)
+
+    def _take_slot(self) -> int:
+        self._cursor = (self._cursor + 1) % self._slots
+        return self._cursor
 
     # ------------------------------------------------------------------------------------------------------
     def _core(self, beta: float, bias: float, scalars: Optional[torch.Tensor], gradient: torch.Tensor, reduce: bool,
@@ -204,10 +225,10 @@ class BoxLoss:
             if block == 0 or not pull:
                 candidates, norms = self.embeddings, self.norms
             else:
-                candidates, norms = self.staged[(block - 1) % 2], self.staged_norms[(block - 1) % 2]
+                candidates, norms = self.staged[(block - 1) % self._slots], self.staged_norms[(block - 1) % self._slots]
             request = None
             if pull and block + 1 < world:
-                slot = block % 2
+                slot = block % self._slots
                 request = PullRequest(self.embeddings.data_ptr(), self.staged[slot].data_ptr(), rows * self.hidden * 2,
                                       self.norms.storage.data_ptr(), self.staged_norms[slot].storage.data_ptr(),
                                       self.staged_norms[slot].nbytes)

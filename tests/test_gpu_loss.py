@@ -266,6 +266,28 @@ def test_pull_inside_the_forward_launch_copies_the_bytes_and_changes_nothing():
     assert torch.equal(outcomes[0][0], outcomes[1][0]) and torch.equal(outcomes[0][1], outcomes[1][1])
 
 
+@pytest.mark.parametrize("world", [1, 2, 5])
+def test_backward_beside_the_next_forward_gives_the_same_bits(world):
+    """With ``overlap_backward`` a block's gradient GEMM runs on a second stream beside the next block's forward kernel,
+    from a second gradient cube and a third staging buffer. Every gradient element still receives its blocks' terms in
+    block order, so gradient and summands equal the in-line run bit for bit, step after step."""
+    from scalingcontrasts_b200.parallel.box import BoxLoss
+
+    rows, hidden = 512, 768
+    ladder = Matryoshka.halvings(hidden, 5)
+    block = normal_embeddings(rows, hidden, seed=11, rank=0).cuda()
+    outcomes = []
+    for overlap in (False, True):
+        engine = BoxLoss(rows, hidden, ladder, LossSpec("pairs"), None, "cuda", overlap_backward=overlap)
+        assert engine.loss.overlap_backward == overlap
+        for _ in range(3):
+            gradient, summands = engine.simulate(block, world)
+        torch.cuda.synchronize()
+        engine.check()
+        outcomes.append((gradient.clone(), summands.clone()))
+    assert torch.equal(outcomes[0][0], outcomes[1][0]) and torch.equal(outcomes[0][1], outcomes[1][1])
+
+
 def test_backward_split_over_candidates_matches_the_single_pass():
     """``backward_split`` divides the candidate range between CTAs that add with float32 reductions in no fixed order:
     the same gradient as the single pass to float32 rounding (and the summands, which do not pass through it, to the bit)."""
