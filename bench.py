@@ -147,6 +147,7 @@ def main() -> int:
 
     # ---- end to end through the public step(): pinned host batches in, loss out, every step --------------------
     e2e_ms = None
+    device_region_end = sampler.mark()
     if not arguments.no_e2e:
         trainer.feed(host_batches[0])
         for step in range(3):
@@ -162,6 +163,8 @@ def main() -> int:
         stop.record()
         fence()
         e2e_ms = start.elapsed_time(stop)
+    e2e_clock = sampler.region(device_region_end).get("sm_mhz")
+    device_clock = sampler.region(0, device_region_end).get("sm_mhz")
     clocks = sampler.stop()
 
     # ---- the loss step alone (outside the timed regions), to separate the blocks' cost from projector and optimizer ----
@@ -235,7 +238,10 @@ def main() -> int:
         if e2e_ms is not None:
             line["e2e"] = {"value": round(cells_per_step_job * steps / (e2e_ms * 1e-3) / 1e9, 2), "unit": "Gcells/s",
                            "ms_per_step": round(e2e_ms / steps, 4),
-                           "h2d_bytes_per_step": trainer.h2d_bytes_per_step(), "d2h_bytes_per_step": trainer.d2h_bytes_per_step()}
+                           "h2d_bytes_per_step": trainer.h2d_bytes_per_step(), "d2h_bytes_per_step": trainer.d2h_bytes_per_step(),
+                           # rank 0's median SM clock in each timed region: the end-to-end loop runs second, on a GPU that
+                           # has been at its power limit for longer
+                           "sm_mhz": e2e_clock, "sm_mhz_device_region": device_clock}
         print(json.dumps(line), flush=True)
     trainer.close()
     if world > 1:

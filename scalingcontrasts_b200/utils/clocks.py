@@ -106,6 +106,10 @@ class ClockSampler:
         """Number of samples taken so far (to cut the record into regions afterwards)."""
         return len(self._samples)
 
+    def region(self, first: int, last: Optional[int] = None) -> Dict[str, object]:
+        """Summary of the samples between two marks (NVML source only; empty otherwise)."""
+        return summarize_samples(self._samples[first:last])
+
     def stop(self) -> Dict[str, object]:
         self._stop.set()
         if self._process is not None:
