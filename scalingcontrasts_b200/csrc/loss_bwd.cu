@@ -7,8 +7,10 @@
 // tensor cores as an MN-major operand (the channels, the GEMM's N, are the contiguous dimension), which needs no copy of
 // the block; or transposed, [H, R], K-major, for callers that hold them that way.
 //
-// A CTA owns one or two 128-row blocks of a strip (two when there are enough strips to fill the GPU): both blocks use
-// the same candidate stage, which halves the candidate refills from L2, the traffic this kernel is bound by.
+// A CTA owns one or two 128-row blocks of a strip and up to 512 tensor-memory columns of accumulators: two blocks x up to
+// 256 channels (both blocks use the same candidate stage, which halves the candidate refills from L2), or, for a band of
+// 257 to 384 channels, one block x the whole band, so that the band's cube, the traffic this kernel is bound by, is read
+// from DRAM once instead of once per 256-channel tile.
 //
 // Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lanes 32*w..), warp 4 TMA producer, warp 5 UMMA issuer
 // and tensor-memory owner. The producer and the issuer run warp-wide with only the TMA / UMMA / commit instructions
@@ -31,11 +33,13 @@ namespace {
 
 constexpr uint32_t bwd_rows = 128;
 constexpr uint32_t bwd_depth = 64;        // candidates per stage
-constexpr uint32_t bwd_max_width = 256;   // channels per tile
+constexpr uint32_t bwd_max_width = 256;   // channels per UMMA and per tile of a two-block CTA
+constexpr uint32_t bwd_wide_width = 384;  // channels of a one-block CTA that takes a whole band
 constexpr uint32_t bwd_stages = 4;                                  // with one row block per CTA; three with two
 constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;        // one 128-row block of the cube
 constexpr uint32_t bwd_b_bytes = bwd_max_width * bwd_depth * 2;
-constexpr uint32_t bwd_stage_bytes = 2 * bwd_a_bytes + bwd_b_bytes; // up to two row blocks share one candidate tile
+constexpr uint32_t bwd_stage_bytes = 2 * bwd_a_bytes + bwd_b_bytes; // two row blocks share one candidate tile
+static_assert(bwd_a_bytes + bwd_wide_width * bwd_depth * 2 <= bwd_stage_bytes, "a wide one-block stage must fit a stage");
 constexpr uint32_t bwd_tmem_columns = 512;
 constexpr uint32_t bwd_block_columns = 256;                         // tensor-memory columns between the two accumulators
 constexpr uint32_t bwd_threads = 192;
@@ -54,6 +58,8 @@ constexpr uint32_t bwd_candidate_maps = 5;                          // boxes of 
 
 struct bwd_tile {
     uint32_t band, channel0, width;
+    uint32_t blocks;    // row blocks per CTA of this tile: 1 or 2
+    uint32_t first_cta; // the tile's CTAs are first_cta .. first_cta + ceil(row blocks / blocks) - 1
 };
 
 // The transposed candidates under five tensor maps that differ only in the box's channel count (16 << index): a tile's
@@ -68,7 +74,6 @@ struct bwd_params {
     uint32_t* status;
     uint32_t rows_q, rows_c, hidden;
     uint32_t tile_count, split;
-    uint32_t blocks_per_cta; // 1 or 2 row blocks of 128
     float scale; // applied to every product before it is added: the loss's 2/N (mirror cell and weight)
     uint64_t budget_ns;
     bwd_tile tiles[bwd_max_tiles];
@@ -89,18 +94,21 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
     bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + 3 * bwd_stage_bytes);
-    // Stage geometry: [row blocks of the cube][candidate tile]: four stages of 48 KB (one 16 KB row block + 32 KB of
-    // candidates) or three of 64 KB (two row blocks).
-    uint32_t const stage_bytes = p.blocks_per_cta * bwd_a_bytes + bwd_b_bytes;
-    uint32_t const stages = p.blocks_per_cta == 2 ? 3u : 4u;
-    uint32_t const b_offset = p.blocks_per_cta * bwd_a_bytes;
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    bwd_tile const tile = p.tiles[blockIdx.y];
-    uint32_t const first_block = blockIdx.x * p.blocks_per_cta;
-    uint32_t const blocks = min(p.blocks_per_cta, p.rows_q / bwd_rows - first_block);
+    uint32_t tile_index = 0;
+    while (tile_index + 1 < p.tile_count && blockIdx.x >= p.tiles[tile_index + 1].first_cta) ++tile_index;
+    bwd_tile const tile = p.tiles[tile_index];
+    // Stage geometry: [row blocks of the cube][candidate tile]: four stages of 48 KB (one 16 KB row block + 32 KB of
+    // candidates) or three of 64 KB (two row blocks + 32 KB, or one row block + 48 KB for a wide tile).
+    bool const wide = tile.width > bwd_max_width;
+    uint32_t const stage_bytes = tile.blocks * bwd_a_bytes + (wide ? bwd_wide_width * bwd_depth * 2 : bwd_b_bytes);
+    uint32_t const stages = stage_bytes > bwd_a_bytes + bwd_b_bytes ? 3u : 4u;
+    uint32_t const b_offset = tile.blocks * bwd_a_bytes;
+    uint32_t const first_block = (blockIdx.x - tile.first_cta) * tile.blocks;
+    uint32_t const blocks = min(tile.blocks, p.rows_q / bwd_rows - first_block);
     uint32_t const chunks_total = p.rows_c / bwd_depth;
     uint32_t const chunks_per_split = (chunks_total + p.split - 1) / p.split;
-    uint32_t const chunk_begin = min(blockIdx.z * chunks_per_split, chunks_total);
+    uint32_t const chunk_begin = min(blockIdx.y * chunks_per_split, chunks_total);
     uint32_t const chunk_end = min(chunk_begin + chunks_per_split, chunks_total);
 
     if (threadIdx.x == 0) {
@@ -168,7 +176,12 @@ __global__ void __launch_bounds__(bwd_threads, 1)
         }
     } else if (warp == 5) {
         bool const elected = elect_one();
-        uint32_t const idesc = umma_idesc_bf16(bwd_rows, tile.width) | (mn_major_ ? umma_idesc_b_mn_major : 0u);
+        // A tile wider than one UMMA's 256 columns is issued in two pieces; the second starts 256 channels on, which is
+        // 32 KB into the candidate stage in either layout (four 8 KB boxes, or 256 rows of 128 bytes).
+        uint32_t const major = mn_major_ ? umma_idesc_b_mn_major : 0u;
+        uint32_t const width0 = wide ? bwd_max_width : tile.width;
+        uint32_t const idesc0 = umma_idesc_bf16(bwd_rows, width0) | major;
+        uint32_t const idesc1 = wide ? (umma_idesc_bf16(bwd_rows, tile.width - bwd_max_width) | major) : 0u;
         constexpr uint32_t descriptor_high = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128-byte swizzle
         uint32_t const low_base = ((stages_base & 0x3FFFFu) >> 4) | (1u << 16);
         // The B operand's leading offset (bits 16-29 of the low word) and its advance per 16 candidates.
@@ -188,9 +201,13 @@ __global__ void __launch_bounds__(bwd_threads, 1)
                     uint64_t a_descriptor, b_descriptor;
                     asm("mov.b64 %0, {%1, %2};" : "=l"(a_descriptor) : "r"(a_low + block * (bwd_a_bytes >> 4) + step * 2u), "r"(descriptor_high));
                     asm("mov.b64 %0, {%1, %2};" : "=l"(b_descriptor) : "r"(b_low + step * b_step), "r"(descriptor_high));
-                    if (elected)
-                        umma_bf16(tmem_base + block * bwd_block_columns, a_descriptor, b_descriptor, idesc,
+                    if (elected) {
+                        umma_bf16(tmem_base + block * bwd_block_columns, a_descriptor, b_descriptor, idesc0,
                                   step == 0 ? accumulate : 1u);
+                        if (wide)
+                            umma_bf16(tmem_base + bwd_max_width, a_descriptor, b_descriptor + ((bwd_max_width * bwd_depth * 2u) >> 4),
+                                      idesc1, step == 0 ? accumulate : 1u);
+                    }
                 }
             }
             accumulate = 1;
@@ -201,7 +218,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
         if (ok && elected) umma_commit(smem_u32(&tail->accumulated));
         __syncwarp();
     } else {
-        if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, blockIdx.y)) {
+        if (mbar_wait(smem_u32(&tail->accumulated), 0u, ctx, site_bwd_accumulated, tile_index)) {
             tcgen05_fence_after();
           for (uint32_t block = 0; block < blocks; ++block) {
             uint32_t const row = (first_block + block) * bwd_rows + warp * 32 + lane;
@@ -248,25 +265,56 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
     p.query_gradient = a.query_gradient, p.status = a.status;
     p.rows_q = a.rows_q, p.rows_c = a.rows_c, p.hidden = a.hidden;
     p.split = a.split, p.budget_ns = a.budget_ns, p.scale = a.scale;
-    uint32_t begin = 0;
+    // Per device, once: the multiprocessor count (a runtime query that needs no context of its own).
+    static int counted_device = -1, multiprocessors = 148;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (counted_device != device) {
+        if (cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) multiprocessors = 148;
+        counted_device = device;
+    }
+    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor with tiles of 256 channels. Only
+    // then (a launch bound by the cube's bytes, not by its tail) does a band of 257..384 channels go to one-block CTAs
+    // that take it whole; a small launch prefers more and shorter CTAs.
+    uint32_t const row_blocks = a.rows_q / bwd_rows;
+    uint32_t plain_tiles = 0, begin = 0;
     for (uint32_t band = 0; band < a.ladder.count; ++band) {
         uint32_t const end = a.ladder.ends[band];
         if (end % 16 || end <= begin) throw std::runtime_error("backward: band edges must ascend in multiples of 16");
-        for (uint32_t channel = begin; channel < end; channel += bwd_max_width) {
+        plain_tiles += (end - begin + bwd_max_width - 1) / bwd_max_width;
+        begin = end;
+    }
+    bool const two_blocks = static_cast<uint64_t>(row_blocks / 2) * plain_tiles * a.split >= 2ull * static_cast<uint64_t>(multiprocessors);
+    begin = 0;
+    for (uint32_t band = 0; band < a.ladder.count; ++band) {
+        uint32_t const end = a.ladder.ends[band];
+        for (uint32_t channel = begin; channel < end;) {
             if (p.tile_count == bwd_max_tiles) throw std::runtime_error("backward: too many channel tiles for one launch");
-            uint32_t const width = end - channel < bwd_max_width ? end - channel : bwd_max_width;
-            p.tiles[p.tile_count++] = bwd_tile{band, channel, width};
+            uint32_t const left = end - channel;
+            bool const whole_band = two_blocks && left == end - begin && left > bwd_max_width && left <= bwd_wide_width;
+            uint32_t const width = whole_band || left <= bwd_max_width ? left : bwd_max_width;
+            p.tiles[p.tile_count++] = bwd_tile{band, channel, width, two_blocks && !whole_band ? 2u : 1u, 0u};
+            channel += width;
         }
         begin = end;
     }
-    // Widest tiles first, and the grid walks the row blocks fastest: the hardware hands out CTAs in that order, so the
-    // long CTAs start first and the short ones fill the tail, while the tiles that read the same band's cube still run
-    // side by side (same row blocks, same pace) and share it through L2.
+    // CTAs go tile by tile, row blocks fastest, in the order the hardware hands them out: two-block tiles before
+    // one-block tiles and wider before narrower. In a large launch the two-block CTAs of the narrow bands wait for DRAM
+    // while the one-block CTAs of a whole wide band are busy with their UMMAs; measured, the launch is fastest with the
+    // latter last (1.832 ms per 16384-row block against 1.861 with them first and 1.860 with both kinds mixed pair of
+    // row blocks by pair).
     for (uint32_t i = 1; i < p.tile_count; ++i)
-        for (uint32_t j = i; j > 0 && p.tiles[j - 1].width < p.tiles[j].width; --j) {
+        for (uint32_t j = i; j > 0 && (p.tiles[j - 1].blocks < p.tiles[j].blocks ||
+                                       (p.tiles[j - 1].blocks == p.tiles[j].blocks && p.tiles[j - 1].width < p.tiles[j].width));
+             --j) {
             bwd_tile const held = p.tiles[j - 1];
             p.tiles[j - 1] = p.tiles[j], p.tiles[j] = held;
         }
+    uint32_t ctas = 0;
+    for (uint32_t i = 0; i < p.tile_count; ++i) {
+        p.tiles[i].first_cta = ctas;
+        ctas += (row_blocks + p.tiles[i].blocks - 1) / p.tiles[i].blocks;
+    }
     bool const mn_major = a.candidates_row_major != nullptr && a.hidden >= 64;
     if (!mn_major && a.transposed_candidates == nullptr) throw std::runtime_error("backward: no candidates given");
     // Everything above is checked before the first driver or runtime call.
@@ -288,22 +336,16 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
             cached_operand_map(a.transposed_candidates, a.rows_c, a.hidden, bwd_depth, channels <= a.hidden ? channels : 16u);
     }
 
-    // Per device, once: the shared-memory limit of the kernel and the multiprocessor count.
-    static int prepared_device = -1, multiprocessors = 148;
-    int device = 0;
-    cudaGetDevice(&device);
+    // Per device, once: the shared-memory limit of the kernel.
+    static int prepared_device = -1;
     if (prepared_device != device) {
         require(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
                 "raising the backward kernel's shared memory");
         require(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_shared_bytes),
                 "raising the backward kernel's shared memory");
-        cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device);
         prepared_device = device;
     }
-    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor.
-    uint32_t const row_blocks = a.rows_q / bwd_rows;
-    p.blocks_per_cta = static_cast<uint64_t>(row_blocks / 2) * p.tile_count * a.split >= 2ull * multiprocessors ? 2 : 1;
-    dim3 const grid((row_blocks + p.blocks_per_cta - 1) / p.blocks_per_cta, p.tile_count, a.split);
+    dim3 const grid(ctas, a.split, 1);
     if (mn_major) backward_kernel<true><<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
     else backward_kernel<false><<<grid, bwd_threads, bwd_shared_bytes, stream>>>(cube_map, candidates, p);
     cudaError_t const error = cudaGetLastError();
