@@ -59,7 +59,8 @@ constexpr uint32_t bwd_candidate_maps = 5;                          // boxes of 
 struct bwd_tile {
     uint32_t band, channel0, width;
     uint32_t blocks;    // row blocks per CTA of this tile: 1 or 2
-    uint32_t first_cta; // the tile's CTAs are first_cta .. first_cta + ceil(row blocks / blocks) - 1
+    uint32_t first_cta; // first CTA of the tile's group; a group's CTAs walk its tiles fastest, then the row blocks
+    uint32_t group;     // tiles in the group: the tiles of one band (they read the same rows of the cube)
 };
 
 // The transposed candidates under five tensor maps that differ only in the box's channel count (16 << index): a tile's
@@ -95,8 +96,12 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
     bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + 3 * bwd_stage_bytes);
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    uint32_t tile_index = 0;
-    while (tile_index + 1 < p.tile_count && blockIdx.x >= p.tiles[tile_index + 1].first_cta) ++tile_index;
+    uint32_t tile_index = 0; // the first tile of the group this CTA falls into, then the CTA's own tile within it
+    while (tile_index + p.tiles[tile_index].group < p.tile_count &&
+           blockIdx.x >= p.tiles[tile_index + p.tiles[tile_index].group].first_cta)
+        tile_index += p.tiles[tile_index].group;
+    uint32_t const within = blockIdx.x - p.tiles[tile_index].first_cta, group = p.tiles[tile_index].group;
+    tile_index += within % group;
     bwd_tile const tile = p.tiles[tile_index];
     // Stage geometry: [row blocks of the cube][candidate tile]: four stages of 48 KB (one 16 KB row block + 32 KB of
     // candidates) or three of 64 KB (two row blocks + 32 KB, or one row block + 48 KB for a wide tile).
@@ -104,7 +109,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const stage_bytes = tile.blocks * bwd_a_bytes + (wide ? bwd_wide_width * bwd_depth * 2 : bwd_b_bytes);
     uint32_t const stages = stage_bytes > bwd_a_bytes + bwd_b_bytes ? 3u : 4u;
     uint32_t const b_offset = tile.blocks * bwd_a_bytes;
-    uint32_t const first_block = (blockIdx.x - tile.first_cta) * tile.blocks;
+    uint32_t const first_block = within / group * tile.blocks;
     uint32_t const blocks = min(tile.blocks, p.rows_q / bwd_rows - first_block);
     uint32_t const chunks_total = p.rows_c / bwd_depth;
     uint32_t const chunks_per_split = (chunks_total + p.split - 1) / p.split;
@@ -293,27 +298,38 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
             uint32_t const left = end - channel;
             bool const whole_band = two_blocks && left == end - begin && left > bwd_max_width && left <= bwd_wide_width;
             uint32_t const width = whole_band || left <= bwd_max_width ? left : bwd_max_width;
-            p.tiles[p.tile_count++] = bwd_tile{band, channel, width, two_blocks && !whole_band ? 2u : 1u, 0u};
+            p.tiles[p.tile_count++] = bwd_tile{band, channel, width, two_blocks && !whole_band ? 2u : 1u, 0u, 1u};
             channel += width;
         }
         begin = end;
     }
-    // CTAs go tile by tile, row blocks fastest, in the order the hardware hands them out: two-block tiles before
-    // one-block tiles and wider before narrower. In a large launch the two-block CTAs of the narrow bands wait for DRAM
+    // CTAs go band by band in the order the hardware hands them out: two-block tiles before one-block tiles and wider
+    // bands before narrower. In a large launch the two-block CTAs of the narrow bands wait for DRAM
     // while the one-block CTAs of a whole wide band are busy with their UMMAs; measured, the launch is fastest with the
     // latter last (1.832 ms per 16384-row block against 1.861 with them first and 1.860 with both kinds mixed pair of
     // row blocks by pair).
+    auto band_width = [&](uint32_t band) { return a.ladder.ends[band] - (band ? a.ladder.ends[band - 1] : 0u); };
+    auto before = [&](bwd_tile const& x, bwd_tile const& y) { // does x go ahead of y?
+        if (x.blocks != y.blocks) return x.blocks > y.blocks;
+        if (x.band != y.band) return band_width(x.band) != band_width(y.band) ? band_width(x.band) > band_width(y.band) : x.band > y.band;
+        return x.width > y.width;
+    };
     for (uint32_t i = 1; i < p.tile_count; ++i)
-        for (uint32_t j = i; j > 0 && (p.tiles[j - 1].blocks < p.tiles[j].blocks ||
-                                       (p.tiles[j - 1].blocks == p.tiles[j].blocks && p.tiles[j - 1].width < p.tiles[j].width));
-             --j) {
+        for (uint32_t j = i; j > 0 && before(p.tiles[j], p.tiles[j - 1]); --j) {
             bwd_tile const held = p.tiles[j - 1];
             p.tiles[j - 1] = p.tiles[j], p.tiles[j] = held;
         }
+    // The tiles of one band read the same rows of the cube. Their CTAs for a row block are handed out one after the
+    // other, so that they run side by side at the pace of the slower one and the second read of a row is served by L2.
     uint32_t ctas = 0;
-    for (uint32_t i = 0; i < p.tile_count; ++i) {
-        p.tiles[i].first_cta = ctas;
-        ctas += (row_blocks + p.tiles[i].blocks - 1) / p.tiles[i].blocks;
+    for (uint32_t i = 0; i < p.tile_count;) {
+        uint32_t members = 1;
+        while (i + members < p.tile_count && p.tiles[i + members].band == p.tiles[i].band &&
+               p.tiles[i + members].blocks == p.tiles[i].blocks)
+            ++members;
+        for (uint32_t m = 0; m < members; ++m) p.tiles[i + m].first_cta = ctas, p.tiles[i + m].group = members;
+        ctas += members * ((row_blocks + p.tiles[i].blocks - 1) / p.tiles[i].blocks);
+        i += members;
     }
     bool const mn_major = a.candidates_row_major != nullptr && a.hidden >= 64;
     if (!mn_major && a.transposed_candidates == nullptr) throw std::runtime_error("backward: no candidates given");
