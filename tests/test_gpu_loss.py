@@ -288,6 +288,34 @@ def test_backward_beside_the_next_forward_gives_the_same_bits(world):
     assert torch.equal(outcomes[0][0], outcomes[1][0]) and torch.equal(outcomes[0][1], outcomes[1][1])
 
 
+def test_overlapped_step_replays_as_a_cuda_graph():
+    """The overlapped step forks onto the plan's two streams and joins them again before it ends, so it can be captured
+    whole; replays give the bits of the eager run."""
+    from scalingcontrasts_b200.parallel.box import BoxLoss
+
+    rows, hidden, world = 512, 768, 4
+    ladder = Matryoshka.halvings(hidden, 5)
+    block = normal_embeddings(rows, hidden, seed=12, rank=0).cuda()
+    engine = BoxLoss(rows, hidden, ladder, LossSpec("pairs"), None, "cuda", overlap_backward=True)
+    gradient, summands = engine.simulate(block, world)
+    torch.cuda.synchronize()
+    expected = (gradient.clone(), summands.clone())
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        engine.simulate(block, world)  # warm-up on the capture stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            engine.simulate(block, world)
+    torch.cuda.current_stream().wait_stream(stream)
+    for _ in range(3):
+        engine.gradient.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        engine.check()
+        assert torch.equal(engine.gradient, expected[0]) and torch.equal(engine.summands, expected[1])
+
+
 def test_backward_split_over_candidates_matches_the_single_pass():
     """``backward_split`` divides the candidate range between CTAs that add with float32 reductions in no fixed order:
     the same gradient as the single pass to float32 rounding (and the summands, which do not pass through it, to the bit)."""
