@@ -58,13 +58,24 @@ __device__ __forceinline__ uint4 pack8(float const (&v)[8]) {
 }
 
 __global__ void __launch_bounds__(256) gelu_forward_kernel(uint4 const* __restrict__ z, uint4* __restrict__ h, size_t vectors) {
+    // Four vectors per thread and trip, all loads issued before the first is used: the pass is bound by memory, and the
+    // arithmetic of one vector would otherwise stand between consecutive loads.
+    constexpr int batch = 4;
     size_t const stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < vectors; index += stride) {
-        float v[8];
-        unpack8(z[index], v);
+    for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < vectors; index += batch * stride) {
+        uint4 loaded[batch];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = gelu_value(v[i]);
-        h[index] = pack8(v);
+        for (int b = 0; b < batch; ++b)
+            if (index + b * stride < vectors) loaded[b] = z[index + b * stride];
+#pragma unroll
+        for (int b = 0; b < batch; ++b) {
+            if (index + b * stride >= vectors) break;
+            float v[8];
+            unpack8(loaded[b], v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = gelu_value(v[i]);
+            h[index + b * stride] = pack8(v);
+        }
     }
 }
 
@@ -81,22 +92,39 @@ __global__ void __launch_bounds__(256)
     uint32_t const vectors_per_row = columns / 8;
     float total[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (column < columns) {
-        for (uint32_t row = first_row + group; row < first_row + tower_rows_per_block && row < rows; row += 8) {
-            size_t const index = static_cast<size_t>(row) * vectors_per_row + column / 8;
-            if (!SC_IN_BOUNDS(index, static_cast<size_t>(rows) * vectors_per_row)) continue;
-            float g[8];
-            unpack8(upstream[index], g);
-            if constexpr (with_activation_) {
-                float v[8];
-                unpack8(z[index], v);
+        // Four rows per trip, their loads issued together; the sums still take the rows in ascending order.
+        constexpr uint32_t batch = 4;
+        uint32_t const end = min(first_row + tower_rows_per_block, rows);
+        for (uint32_t base = first_row + group; base < end; base += 8 * batch) {
+            uint4 up[batch], pre[batch];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) g[i] *= gelu_slope(v[i]);
-                uint4 const rounded = pack8(g);
-                out[index] = rounded;
-                unpack8(rounded, g); // the bias gradient sums what the weight-gradient GEMM will read
+            for (uint32_t b = 0; b < batch; ++b) {
+                uint32_t const row = base + 8 * b;
+                size_t const index = static_cast<size_t>(row) * vectors_per_row + column / 8;
+                if (row < end && SC_IN_BOUNDS(index, static_cast<size_t>(rows) * vectors_per_row)) {
+                    up[b] = upstream[index];
+                    if constexpr (with_activation_) pre[b] = z[index];
+                }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) total[i] += g[i];
+            for (uint32_t b = 0; b < batch; ++b) {
+                uint32_t const row = base + 8 * b;
+                size_t const index = static_cast<size_t>(row) * vectors_per_row + column / 8;
+                if (row >= end || !SC_IN_BOUNDS(index, static_cast<size_t>(rows) * vectors_per_row)) continue;
+                float g[8];
+                unpack8(up[b], g);
+                if constexpr (with_activation_) {
+                    float v[8];
+                    unpack8(pre[b], v);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) g[i] *= gelu_slope(v[i]);
+                    uint4 const rounded = pack8(g);
+                    out[index] = rounded;
+                    unpack8(rounded, g); // the bias gradient sums what the weight-gradient GEMM will read
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) total[i] += g[i];
+            }
         }
     }
 #pragma unroll
