@@ -6,6 +6,8 @@
 // block passed to the kernel.
 #pragma once
 
+#include <array>
+#include <vector>
 #include <cstddef>
 #include <cstdint>
 #include <string>
@@ -156,6 +158,11 @@ struct backward_arguments {
     uint64_t budget_ns;
 };
 void launch_backward(backward_arguments const& arguments, cudaStream_t stream);
+// The backward launch's tile table for a shape, without launching: one {band, first channel, width, row blocks per CTA,
+// first CTA of the tile's group, tiles in the group} per tile in grid order, and the grid's CTA count. A group's CTAs
+// walk its tiles fastest, then the row blocks.
+std::vector<std::array<uint32_t, 6>> backward_plan(uint32_t rows_q, ladder_host const& ladder, uint32_t split,
+                                                    int multiprocessors, uint32_t* ctas);
 
 void preload_loss_kernels();
 

@@ -369,6 +369,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         sc::bounds_record_collectives(records[3].data());
         return records;
     });
+    m.def("backward_plan", [](uint32_t rows_q, std::vector<uint32_t> const& ends, uint32_t split, int multiprocessors) {
+        uint32_t ctas = 0;
+        auto const tiles = sc::backward_plan(rows_q, ladder_of(ends), split, multiprocessors, &ctas);
+        return py::make_tuple(tiles, ctas);
+    }, py::arg("rows_q"), py::arg("ends"), py::arg("split") = 1, py::arg("multiprocessors") = 148);
     m.def("note_launches", [](uint64_t count) { sc::note_launch(count); });
     m.def("forward_partial_slots", &sc::forward_partial_slots);
     m.def("forward_quantities", &sc::forward_quantities);

@@ -20,8 +20,10 @@
 // is deterministic; with a larger split the candidate range is divided and the order of a launch's partial sums is not.
 //
 // Parity: backward_tile_cuda_ (scalingcontrasts.cuh:1042-1136).
+#include <array>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "api.h"
 #include "common.cuh"
@@ -260,6 +262,67 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     }
 }
 
+// The launch's tile table: which (band, channels, row blocks per CTA) tiles there are and which CTAs of the
+// one-dimensional grid belong to each. Pure arithmetic on the shape, so that it can be checked without a GPU.
+uint32_t plan_tiles(uint32_t rows_q, ladder_host const& ladder, uint32_t split, int multiprocessors, bwd_tile* tiles,
+                    uint32_t& tile_count) {
+    tile_count = 0;
+    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor with tiles of 256 channels. Only
+    // then (a launch bound by the cube's bytes, not by its tail) does a band of 257..384 channels go to one-block CTAs
+    // that take it whole; a small launch prefers more and shorter CTAs.
+    uint32_t const row_blocks = rows_q / bwd_rows;
+    uint32_t plain_tiles = 0, begin = 0;
+    for (uint32_t band = 0; band < ladder.count; ++band) {
+        uint32_t const end = ladder.ends[band];
+        if (end % 16 || end <= begin) throw std::runtime_error("backward: band edges must ascend in multiples of 16");
+        plain_tiles += (end - begin + bwd_max_width - 1) / bwd_max_width;
+        begin = end;
+    }
+    bool const two_blocks = static_cast<uint64_t>(row_blocks / 2) * plain_tiles * split >= 2ull * static_cast<uint64_t>(multiprocessors);
+    begin = 0;
+    for (uint32_t band = 0; band < ladder.count; ++band) {
+        uint32_t const end = ladder.ends[band];
+        for (uint32_t channel = begin; channel < end;) {
+            if (tile_count == bwd_max_tiles) throw std::runtime_error("backward: too many channel tiles for one launch");
+            uint32_t const left = end - channel;
+            bool const whole_band = two_blocks && left == end - begin && left > bwd_max_width && left <= bwd_wide_width;
+            uint32_t const width = whole_band || left <= bwd_max_width ? left : bwd_max_width;
+            tiles[tile_count++] = bwd_tile{band, channel, width, two_blocks && !whole_band ? 2u : 1u, 0u, 1u};
+            channel += width;
+        }
+        begin = end;
+    }
+    // CTAs go band by band in the order the hardware hands them out: two-block tiles before one-block tiles and wider
+    // bands before narrower. In a large launch the two-block CTAs of the narrow bands wait for DRAM
+    // while the one-block CTAs of a whole wide band are busy with their UMMAs; measured, the launch is fastest with the
+    // latter last (1.832 ms per 16384-row block against 1.861 with them first and 1.860 with both kinds mixed pair of
+    // row blocks by pair).
+    auto band_width = [&](uint32_t band) { return ladder.ends[band] - (band ? ladder.ends[band - 1] : 0u); };
+    auto before = [&](bwd_tile const& x, bwd_tile const& y) { // does x go ahead of y?
+        if (x.blocks != y.blocks) return x.blocks > y.blocks;
+        if (x.band != y.band) return band_width(x.band) != band_width(y.band) ? band_width(x.band) > band_width(y.band) : x.band > y.band;
+        return x.width > y.width;
+    };
+    for (uint32_t i = 1; i < tile_count; ++i)
+        for (uint32_t j = i; j > 0 && before(tiles[j], tiles[j - 1]); --j) {
+            bwd_tile const held = tiles[j - 1];
+            tiles[j - 1] = tiles[j], tiles[j] = held;
+        }
+    // The tiles of one band read the same rows of the cube. Their CTAs for a row block are handed out one after the
+    // other, so that they run side by side at the pace of the slower one and the second read of a row is served by L2.
+    uint32_t ctas = 0;
+    for (uint32_t i = 0; i < tile_count;) {
+        uint32_t members = 1;
+        while (i + members < tile_count && tiles[i + members].band == tiles[i].band &&
+               tiles[i + members].blocks == tiles[i].blocks)
+            ++members;
+        for (uint32_t m = 0; m < members; ++m) tiles[i + m].first_cta = ctas, tiles[i + m].group = members;
+        ctas += members * ((row_blocks + tiles[i].blocks - 1) / tiles[i].blocks);
+        i += members;
+    }
+    return ctas;
+}
+
 } // namespace
 
 void launch_backward(backward_arguments const& a, cudaStream_t stream) {
@@ -278,59 +341,7 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
         if (cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) multiprocessors = 148;
         counted_device = device;
     }
-    // Two row blocks per CTA once that still leaves at least two CTAs per multiprocessor with tiles of 256 channels. Only
-    // then (a launch bound by the cube's bytes, not by its tail) does a band of 257..384 channels go to one-block CTAs
-    // that take it whole; a small launch prefers more and shorter CTAs.
-    uint32_t const row_blocks = a.rows_q / bwd_rows;
-    uint32_t plain_tiles = 0, begin = 0;
-    for (uint32_t band = 0; band < a.ladder.count; ++band) {
-        uint32_t const end = a.ladder.ends[band];
-        if (end % 16 || end <= begin) throw std::runtime_error("backward: band edges must ascend in multiples of 16");
-        plain_tiles += (end - begin + bwd_max_width - 1) / bwd_max_width;
-        begin = end;
-    }
-    bool const two_blocks = static_cast<uint64_t>(row_blocks / 2) * plain_tiles * a.split >= 2ull * static_cast<uint64_t>(multiprocessors);
-    begin = 0;
-    for (uint32_t band = 0; band < a.ladder.count; ++band) {
-        uint32_t const end = a.ladder.ends[band];
-        for (uint32_t channel = begin; channel < end;) {
-            if (p.tile_count == bwd_max_tiles) throw std::runtime_error("backward: too many channel tiles for one launch");
-            uint32_t const left = end - channel;
-            bool const whole_band = two_blocks && left == end - begin && left > bwd_max_width && left <= bwd_wide_width;
-            uint32_t const width = whole_band || left <= bwd_max_width ? left : bwd_max_width;
-            p.tiles[p.tile_count++] = bwd_tile{band, channel, width, two_blocks && !whole_band ? 2u : 1u, 0u, 1u};
-            channel += width;
-        }
-        begin = end;
-    }
-    // CTAs go band by band in the order the hardware hands them out: two-block tiles before one-block tiles and wider
-    // bands before narrower. In a large launch the two-block CTAs of the narrow bands wait for DRAM
-    // while the one-block CTAs of a whole wide band are busy with their UMMAs; measured, the launch is fastest with the
-    // latter last (1.832 ms per 16384-row block against 1.861 with them first and 1.860 with both kinds mixed pair of
-    // row blocks by pair).
-    auto band_width = [&](uint32_t band) { return a.ladder.ends[band] - (band ? a.ladder.ends[band - 1] : 0u); };
-    auto before = [&](bwd_tile const& x, bwd_tile const& y) { // does x go ahead of y?
-        if (x.blocks != y.blocks) return x.blocks > y.blocks;
-        if (x.band != y.band) return band_width(x.band) != band_width(y.band) ? band_width(x.band) > band_width(y.band) : x.band > y.band;
-        return x.width > y.width;
-    };
-    for (uint32_t i = 1; i < p.tile_count; ++i)
-        for (uint32_t j = i; j > 0 && before(p.tiles[j], p.tiles[j - 1]); --j) {
-            bwd_tile const held = p.tiles[j - 1];
-            p.tiles[j - 1] = p.tiles[j], p.tiles[j] = held;
-        }
-    // The tiles of one band read the same rows of the cube. Their CTAs for a row block are handed out one after the
-    // other, so that they run side by side at the pace of the slower one and the second read of a row is served by L2.
-    uint32_t ctas = 0;
-    for (uint32_t i = 0; i < p.tile_count;) {
-        uint32_t members = 1;
-        while (i + members < p.tile_count && p.tiles[i + members].band == p.tiles[i].band &&
-               p.tiles[i + members].blocks == p.tiles[i].blocks)
-            ++members;
-        for (uint32_t m = 0; m < members; ++m) p.tiles[i + m].first_cta = ctas, p.tiles[i + m].group = members;
-        ctas += members * ((row_blocks + p.tiles[i].blocks - 1) / p.tiles[i].blocks);
-        i += members;
-    }
+    uint32_t const ctas = plan_tiles(a.rows_q, a.ladder, a.split, multiprocessors, p.tiles, p.tile_count);
     bool const mn_major = a.candidates_row_major != nullptr && a.hidden >= 64;
     if (!mn_major && a.transposed_candidates == nullptr) throw std::runtime_error("backward: no candidates given");
     // Everything above is checked before the first driver or runtime call.
@@ -370,6 +381,19 @@ void launch_backward(backward_arguments const& a, cudaStream_t stream) {
 }
 
 void preload_forward_kernels();
+std::vector<std::array<uint32_t, 6>> backward_plan(uint32_t rows_q, ladder_host const& ladder, uint32_t split,
+                                                    int multiprocessors, uint32_t* ctas) {
+    if (rows_q % bwd_rows || split < 1) throw std::runtime_error("backward_plan: rows must be a multiple of 128 and split positive");
+    bwd_tile tiles[bwd_max_tiles];
+    uint32_t count = 0;
+    uint32_t const total = plan_tiles(rows_q, ladder, split, multiprocessors, tiles, count);
+    if (ctas) *ctas = total;
+    std::vector<std::array<uint32_t, 6>> out;
+    for (uint32_t i = 0; i < count; ++i)
+        out.push_back({tiles[i].band, tiles[i].channel0, tiles[i].width, tiles[i].blocks, tiles[i].first_cta, tiles[i].group});
+    return out;
+}
+
 SC_DEFINE_BOUNDS_READER(bounds_record_backward)
 
 void preload_loss_kernels() {
