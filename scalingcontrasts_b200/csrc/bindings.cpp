@@ -107,6 +107,9 @@ struct loss_plan {
     uint32_t pending_slot = 0;
     sc::backward_arguments pending_backward{};
 
+    loss_plan() = default;
+    loss_plan(loss_plan const&) = delete; // owns streams and events
+    loss_plan& operator=(loss_plan const&) = delete;
     ~loss_plan() {
         for (cudaEvent_t event : {forward_done[0], forward_done[1], backward_done[0], backward_done[1], forked[0], forked[1],
                                   rejoined[0], rejoined[1]})
