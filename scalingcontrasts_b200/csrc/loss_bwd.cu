@@ -37,7 +37,7 @@ constexpr uint32_t bwd_rows = 128;
 constexpr uint32_t bwd_depth = 64;        // candidates per stage
 constexpr uint32_t bwd_max_width = 256;   // channels per UMMA and per tile of a two-block CTA
 constexpr uint32_t bwd_wide_width = 384;  // channels of a one-block CTA that takes a whole band
-constexpr uint32_t bwd_stages = 4;                                  // with one row block per CTA; three with two
+constexpr uint32_t bwd_stages = 6;                                  // at most
 constexpr uint32_t bwd_a_bytes = bwd_rows * bwd_depth * 2;        // one 128-row block of the cube
 constexpr uint32_t bwd_b_bytes = bwd_max_width * bwd_depth * 2;
 constexpr uint32_t bwd_stage_bytes = 2 * bwd_a_bytes + bwd_b_bytes; // two row blocks share one candidate tile
@@ -54,8 +54,11 @@ struct bwd_tail {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-constexpr uint32_t bwd_shared_bytes = 1024 + 3 * bwd_stage_bytes + sizeof(bwd_tail);
-static_assert(4 * (bwd_a_bytes + bwd_b_bytes) <= 3 * bwd_stage_bytes, "four one-block stages must fit where three two-block stages do");
+// The ring of stages: 208 KB; a stage is the CTA's row blocks of the cube plus the candidates of the tile's own width.
+constexpr uint32_t bwd_ring_bytes = 208 * 1024;
+constexpr uint32_t bwd_shared_bytes = 1024 + bwd_ring_bytes + sizeof(bwd_tail);
+static_assert(3 * bwd_stage_bytes <= bwd_ring_bytes, "three of the largest stages must fit the ring");
+static_assert(bwd_shared_bytes <= 227 * 1024, "the kernel's shared memory must fit one CTA's maximum");
 constexpr uint32_t bwd_candidate_maps = 5;                          // boxes of 16, 32, 64, 128 and 256 channels
 
 struct bwd_tile {
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     extern __shared__ uint8_t raw_shared[];
     uint32_t const raw_address = smem_u32(raw_shared);
     uint32_t const stages_base = (raw_address + 1023u) & ~1023u;
-    bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + 3 * bwd_stage_bytes);
+    bwd_tail* tail = reinterpret_cast<bwd_tail*>(raw_shared + (stages_base - raw_address) + bwd_ring_bytes);
     uint32_t const warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     uint32_t tile_index = 0; // the first tile of the group this CTA falls into, then the CTA's own tile within it
     while (tile_index + p.tiles[tile_index].group < p.tile_count &&
@@ -105,11 +108,16 @@ __global__ void __launch_bounds__(bwd_threads, 1)
     uint32_t const within = blockIdx.x - p.tiles[tile_index].first_cta, group = p.tiles[tile_index].group;
     tile_index += within % group;
     bwd_tile const tile = p.tiles[tile_index];
-    // Stage geometry: [row blocks of the cube][candidate tile]: four stages of 48 KB (one 16 KB row block + 32 KB of
-    // candidates) or three of 64 KB (two row blocks + 32 KB, or one row block + 48 KB for a wide tile).
+    // Stage geometry: [row blocks of the cube, 16 KB each][candidate tile of the tile's width]. MN-major candidates come in
+    // whole boxes of 64 channels (8 KB), K-major ones in rows of 128 bytes per channel; either way a stage is a multiple of
+    // 1 KB, so every stage starts on a swizzle atom.
     bool const wide = tile.width > bwd_max_width;
-    uint32_t const stage_bytes = tile.blocks * bwd_a_bytes + (wide ? bwd_wide_width * bwd_depth * 2 : bwd_b_bytes);
-    uint32_t const stages = stage_bytes > bwd_a_bytes + bwd_b_bytes ? 3u : 4u;
+    uint32_t const candidate_bytes = mn_major_ ? ((tile.width + 63u) / 64u) * bwd_mn_box_bytes : tile.width * bwd_depth * 2u;
+    uint32_t const stage_bytes = tile.blocks * bwd_a_bytes + candidate_bytes;
+    // One-block tiles (small launches) take as deep a ring as fits: 0.187 -> 0.181 ms per 4096-row block. Two-block tiles
+    // stay at three stages: deeper rings for the narrow, DRAM-bound ones made a 16384-row launch slower (1.82 -> 1.85 ms per
+    // block), their CTAs then take bandwidth from the wide ones that finish last.
+    uint32_t const stages = tile.blocks == 2 ? 3u : min(bwd_stages, bwd_ring_bytes / stage_bytes);
     uint32_t const b_offset = tile.blocks * bwd_a_bytes;
     uint32_t const first_block = within / group * tile.blocks;
     uint32_t const blocks = min(tile.blocks, p.rows_q / bwd_rows - first_block);
