@@ -40,12 +40,17 @@ class _DeviceLoss(torch.autograd.Function):
         kept = summands.clone()  # the payload is rewritten by the next step
         ctx.save_for_backward(gradient, kept)
         ctx.input_dtype = embeddings.dtype
+        ctx.unit_upstream = bool(module.unit_upstream)
         module.last_summands = kept
         return kept[0].clone()
 
     @staticmethod
     def backward(ctx, grad_output):
         gradient, summands = ctx.saved_tensors
+        if ctx.unit_upstream:
+            # The caller promised `loss.backward()` with nothing after the loss: the upstream gradient is one, and a pass
+            # over the row gradients that multiplies them by it (25 MB in, 25 MB out per step) is left out.
+            return gradient.to(ctx.input_dtype), summands[2], summands[1], None
         scaled = gradient * grad_output.to(gradient.dtype)
         return scaled.to(ctx.input_dtype), summands[2] * grad_output, summands[1] * grad_output, None
 
@@ -106,6 +111,10 @@ class MatryoshkaSigmoidLoss(nn.Module):
         self.logit_scale = nn.Parameter(torch.tensor(init_logit_scale, dtype=torch.float32, device=device))
         self.logit_bias = nn.Parameter(torch.tensor(init_logit_bias, dtype=torch.float32, device=device))
         self.last_summands: Optional[torch.Tensor] = None
+        # Set by a caller that differentiates the loss itself with an upstream gradient of one (``loss.backward()``): the
+        # GPU path then hands the row gradients on without scaling them. Anything that scales or combines the loss before
+        # differentiating must leave it False.
+        self.unit_upstream = False
         self.engine = None
         if device.type == "cuda":
             from ..parallel.box import BoxLoss

@@ -42,6 +42,7 @@ class ContrastiveTrainer:
         # The loss step after its publish pass is the same kernel sequence over the same buffers every time: replayed as
         # a CUDA graph it costs the host two launches however many peers are scored.
         self.loss.engine.use_graphs = graphs
+        self.loss.unit_upstream = True  # step_on_device() calls loss.backward() on the bare loss
         # Every rank's loss is the world's sum and row gradients are final, so parameter gradients are summed.
         self.reducer = GradientReducer(self.projector.parameters(), self.domain, scale=1.0)
         self.projector.gradient_landing = self.reducer.landing_buffers(self.projector) or None

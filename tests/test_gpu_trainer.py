@@ -55,3 +55,23 @@ def test_a_recorded_timeout_surfaces_with_the_next_loss():
     with pytest.raises(RuntimeError, match="bounded device wait"):
         trainer.last_loss()
     trainer.close()
+
+
+def test_unit_upstream_hands_the_same_gradients_on():
+    """``unit_upstream`` skips the multiplication of the row gradients by the upstream gradient of ``loss.backward()``,
+    which is one: parameter and input gradients are the same bits with and without it."""
+    from scalingcontrasts_b200 import MatryoshkaSigmoidLoss
+
+    rows, hidden = 256, 256
+    outcomes = []
+    for unit in (False, True):
+        torch.manual_seed(3)
+        criterion = MatryoshkaSigmoidLoss(rows, hidden, prefixes=3, device="cuda")
+        criterion.unit_upstream = unit
+        embeddings = torch.randn(rows, hidden, device="cuda").to(torch.bfloat16).requires_grad_(True)
+        loss = criterion(embeddings)
+        loss.backward()
+        torch.cuda.synchronize()
+        outcomes.append((embeddings.grad.clone(), criterion.logit_scale.grad.clone(), criterion.logit_bias.grad.clone(), loss.detach().clone()))
+    for a, b in zip(*outcomes):
+        assert torch.equal(a, b)
