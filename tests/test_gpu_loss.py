@@ -394,3 +394,32 @@ def test_backward_reads_row_major_candidates_like_transposed_ones(ext, rows, hid
     assert relative_l2(outcomes[0], reference) < 1e-5
     assert relative_l2(outcomes[1], reference) < 1e-5
     assert relative_l2(outcomes[1], outcomes[0]) < 1e-6
+
+
+@pytest.mark.parametrize("hidden,ends", [(768, (48, 96, 192, 384, 768)), (1024, (64, 128, 256, 512, 1024)),
+                                         (1104, (16, 32, 336, 1104))])
+def test_backward_of_a_large_launch_with_an_odd_number_of_row_blocks(ext, hidden, ends):
+    """12928 query rows are 101 row blocks: enough for the large-launch tiling (two row blocks per CTA, a band of 257 to
+    384 channels in one-block CTAs that take it whole, the tiles of a wider band side by side in the grid) and an odd
+    count, so the last two-block CTA of every tile owns a single block. Few candidates keep the cube small. Both operand
+    layouts against the float32 matmul."""
+    _float32_matmul_exact()
+    rows_q, rows_c = 12928, 128
+    tiles, ctas = ext.backward_plan(rows_q, list(ends), 1, torch.cuda.get_device_properties(0).multi_processor_count)
+    assert any(tile[3] == 2 for tile in tiles)  # the large-launch tiling is what runs
+    stream = torch.cuda.current_stream().cuda_stream
+    generator = torch.Generator(device="cuda").manual_seed(6)
+    cube = (torch.randn(len(ends), rows_q, rows_c, device="cuda", generator=generator) * 0.1).to(torch.bfloat16)
+    candidates = torch.randn(rows_c, hidden, device="cuda", generator=generator).to(torch.bfloat16)
+    transposed = candidates.T.contiguous()
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    reference = 0.5 * torch.cat([cube[b].float() @ candidates.float()[:, (0 if b == 0 else ends[b - 1]):ends[b]]
+                                 for b in range(len(ends))], dim=1)
+    for row_major in (0, candidates.data_ptr()):
+        gradient = torch.zeros(rows_q, hidden, device="cuda")
+        ext.backward(cube.data_ptr(), transposed.data_ptr() if row_major == 0 else 0, gradient.data_ptr(), status.data_ptr(),
+                     rows_q, rows_c, hidden, list(ends), 1, 0.5, 2_000_000_000, stream, row_major=row_major)
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0
+        assert relative_l2(gradient, reference) < 1e-5
+        assert relative_l2(gradient[-128:], reference[-128:]) < 1e-5  # the odd last row block
