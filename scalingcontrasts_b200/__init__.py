@@ -21,6 +21,7 @@ _LAZY = {
     "Projector": ("scalingcontrasts_b200.models.projector", "Projector"),
     "GradientReducer": ("scalingcontrasts_b200.parallel.reducer", "GradientReducer"),
     "ContrastiveTrainer": ("scalingcontrasts_b200.trainer", "ContrastiveTrainer"),
+    "FusedAdamW": ("scalingcontrasts_b200.optim", "FusedAdamW"),
     "RdmaRail": ("scalingcontrasts_b200.parallel.rail", "RdmaRail"),
 }
 

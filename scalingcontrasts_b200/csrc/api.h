@@ -177,6 +177,22 @@ void launch_gelu_backward_bias(void const* upstream_bf16, void const* z_bf16, vo
 void launch_column_sums(void const* matrix_bf16, float* partials, void* sums_bf16, uint32_t rows, uint32_t columns,
                         cudaStream_t stream);
 
+// -------- optimizer (optim.cu) -----------------------------------------------------------------------------------
+// AdamW with decoupled weight decay over a list of tensors, eight per launch. Parameters and gradients bfloat16 or
+// float32 (the same type for a tensor's pair), both moments float32. `step` counts from 1.
+constexpr uint32_t adamw_max_tensors = 8;
+struct adamw_tensor {
+    void* param;
+    void const* grad;
+    float* exp_avg;
+    float* exp_avg_sq;
+    size_t count;
+    uint32_t is_bf16;
+    uint32_t vectorised; // set by the launcher: 16-byte loads apply
+};
+void launch_adamw(adamw_tensor const* tensors, uint32_t count, float lr, float beta1, float beta2, float eps, float decay,
+                  uint64_t step, cudaStream_t stream);
+
 // -------- bounds-checked debug build ----------------------------------------------------------------------------
 // True in the build with -DSC_BOUNDS=1, in which kernels compare every computed global index with its limit. The
 // readers copy out the first recorded miss of each translation unit (eight words, all zero when there was none; always
@@ -187,6 +203,7 @@ void bounds_record_forward(uint32_t* out);
 void bounds_record_backward(uint32_t* out);
 void bounds_record_collectives(uint32_t* out);
 void bounds_record_tower(uint32_t* out);
+void bounds_record_optim(uint32_t* out);
 
 // -------- oracle twin (oracle_cpu.cpp) ---------------------------------------------------------------------------
 // Plain triple loop in float64; gradient [n, hidden]; out[0]=loss, out[1]=bias grad, out[2]=log-beta grad,

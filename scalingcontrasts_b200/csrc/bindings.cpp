@@ -364,8 +364,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("BOUNDS_BUILD") = sc::bounds_build();
     m.def("bounds_records", []() {
         // the first out-of-range index each translation unit recorded (all zeros: none); ordinary builds never record
-        std::vector<std::vector<uint32_t>> records(5, std::vector<uint32_t>(8, 0u));
+        std::vector<std::vector<uint32_t>> records(6, std::vector<uint32_t>(8, 0u));
         sc::bounds_record_tower(records[4].data());
+        sc::bounds_record_optim(records[5].data());
         sc::bounds_record_small(records[0].data());
         sc::bounds_record_forward(records[1].data());
         sc::bounds_record_backward(records[2].data());
@@ -377,6 +378,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         auto const tiles = sc::backward_plan(rows_q, ladder_of(ends), split, multiprocessors, &ctas);
         return py::make_tuple(tiles, ctas);
     }, py::arg("rows_q"), py::arg("ends"), py::arg("split") = 1, py::arg("multiprocessors") = 148);
+    m.def("adamw_step",
+          [](std::vector<std::tuple<uint64_t, uint64_t, uint64_t, uint64_t, uint64_t, bool>> const& entries, float lr,
+             float beta1, float beta2, float eps, float weight_decay, uint64_t step, uint64_t stream) {
+              // one entry per tensor: (parameter, gradient, first moment, second moment, element count, is bfloat16)
+              std::vector<sc::adamw_tensor> tensors;
+              for (auto const& [param, grad, exp_avg, exp_avg_sq, count, is_bf16] : entries)
+                  tensors.push_back(sc::adamw_tensor{pointer<void>(param), pointer<void>(grad), pointer<float>(exp_avg),
+                                                     pointer<float>(exp_avg_sq), static_cast<size_t>(count), is_bf16 ? 1u : 0u, 0u});
+              sc::launch_adamw(tensors.data(), static_cast<uint32_t>(tensors.size()), lr, beta1, beta2, eps, weight_decay, step,
+                               stream_of(stream));
+          },
+          py::arg("entries"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"),
+          py::arg("step"), py::arg("stream"));
     m.def("note_launches", [](uint64_t count) { sc::note_launch(count); });
     m.def("forward_partial_slots", &sc::forward_partial_slots);
     m.def("forward_quantities", &sc::forward_quantities);

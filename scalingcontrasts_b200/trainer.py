@@ -48,11 +48,15 @@ class ContrastiveTrainer:
         self.projector.gradient_landing = self.reducer.landing_buffers(self.projector) or None
         parameters = list(self.projector.parameters()) + list(self.loss.parameters())
         if optimizer == "adamw":
+            from .optim import FusedAdamW
+
+            self.optimizer = FusedAdamW(parameters, lr=lr, weight_decay=weight_decay)  # one own launch per step
+        elif optimizer == "adamw-torch":
             self.optimizer = torch.optim.AdamW(parameters, lr=lr, weight_decay=weight_decay, fused=True)
         elif optimizer == "sgd":
             self.optimizer = torch.optim.SGD(parameters, lr=lr, momentum=0.9)
         else:
-            raise ValueError("optimizer must be adamw or sgd")
+            raise ValueError("optimizer must be adamw, adamw-torch or sgd")
         self.steps_done = 0
         self._copy_stream = torch.cuda.Stream(device=self.device)
         self._slots = [torch.empty(rows, in_features, dtype=torch.bfloat16, device=self.device) for _ in range(2)]

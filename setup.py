@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join("scalingcontrasts_b200", "csrc")
 SOURCES = [os.path.join(CSRC, name) for name in (
     "bindings.cpp", "domain.cpp", "oracle_cpu.cpp", "rail.cpp",
-    "collectives.cu", "loss_small.cu", "loss_fwd.cu", "loss_bwd.cu", "no_alloc.cu", "tower.cu",
+    "collectives.cu", "loss_small.cu", "loss_fwd.cu", "loss_bwd.cu", "no_alloc.cu", "tower.cu", "optim.cu",
 )]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr"]
 # Tuning knob of the forward kernel (16 or 8 epilogue warps); the default is the measured best.

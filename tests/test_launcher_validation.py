@@ -54,3 +54,14 @@ def test_the_ordinary_build_is_not_the_bounds_checked_one(ext):
 
     assert bool(ext.BOUNDS_BUILD) == (os.environ.get("SC_NATIVE_VARIANT", "") == "bounds")
     assert all(word == 0 for record in ext.bounds_records() for word in record) or bool(ext.BOUNDS_BUILD)
+
+
+@pytest.mark.parametrize("entries,step,betas,message", [
+    ([(256, 256, 256, 256, 8, True)], 0, (0.9, 0.999), "starts at 1"),
+    ([(256, 256, 256, 256, 8, True)], 1, (1.0, 0.999), "betas"),
+    ([(0, 256, 256, 256, 8, True)], 1, (0.9, 0.999), "null pointer"),
+    ([(256, 256, 256, 256, 0, False)], 1, (0.9, 0.999), "empty tensor"),
+])
+def test_adamw_refuses_bad_arguments(ext, entries, step, betas, message):
+    with pytest.raises(RuntimeError, match=message):
+        ext.adamw_step(entries, 1e-3, betas[0], betas[1], 1e-8, 0.0, step, 0)
