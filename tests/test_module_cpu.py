@@ -57,3 +57,15 @@ def test_roofline_columns_use_the_measured_file_or_say_fallback(tmp_path, monkey
     flops = 2.0 * 1536 * 16384 * 131072
     assert abs(loss_step_roofline_ms(16384, 8, 768, peaks) - flops / (1400.0 * 1e12) * 1e3) < 1e-9
     assert abs(loss_step_roofline_ms(16384, 8, 768, peaks, sustained=False) - flops / (1600.0 * 1e12) * 1e3) < 1e-9
+
+
+def test_fused_adamw_refuses_what_its_kernel_cannot_take():
+    import pytest
+    import torch
+
+    from scalingcontrasts_b200.optim import FusedAdamW
+
+    with pytest.raises(ValueError, match="at least one"):
+        FusedAdamW([])
+    with pytest.raises(ValueError, match="contiguous CUDA parameters"):
+        FusedAdamW([torch.zeros(4, requires_grad=True)])  # a CPU tensor
