@@ -75,3 +75,20 @@ def test_bad_ladders_are_refused():
     for ends in ([48, 40, 768], [24, 768], [64, 64]):
         with pytest.raises(RuntimeError):
             ext.backward_plan(1024, ends, 1, 148)
+
+
+@pytest.mark.parametrize("rows_q,rows_c", [(128, 128), (1024, 1024), (4096, 4096), (16384, 16384), (16384, 128), (128, 16384),
+                                           (12928, 4096)])
+def test_forward_run_length_divides_the_tiles_and_sizes_the_partial_records(rows_q, rows_c):
+    """The forward kernel's work items are (strip of 128 rows, run of consecutive 64-candidate tiles). The chosen run
+    length must divide a strip's tiles, and one partial record exists per (run, column group of the epilogue)."""
+    ext = native()
+    column_tiles = rows_c // 64
+    for multiprocessors in (4, 148):
+        run = ext.forward_choose_tiles_per_run(rows_q, rows_c, multiprocessors)
+        assert run >= 1 and column_tiles % run == 0
+        slots = ext.forward_partial_slots(rows_c, run)
+        assert slots % (column_tiles // run) == 0 and slots // (column_tiles // run) in (2, 4)  # 8 or 16 epilogue warps
+        fused_run = ext.forward_choose_tiles_per_run_fused(rows_q, rows_c, multiprocessors)
+        assert 1 <= fused_run <= 16 and column_tiles % fused_run == 0
+    assert ext.forward_quantities(5) == 12
